@@ -1,0 +1,183 @@
+/*
+ * qwengine_attn.h -- C ABI of the B200 (sm_100a) full-attention mixer.
+ *
+ * The reference engine has no separately linked attention library: its forward
+ * passes launch five kernels inline (paths below are relative to the reference
+ * project root).  Each "per-kernel launcher" here takes the argument list of one
+ * of those launch sites, in the same order, with the <<<grid, block, 0, stream>>>
+ * replaced by a trailing row count and stream, so a maintainer can swap the
+ * inline launch for one call.  Every function returns 0 on success or a QW_ERR_*
+ * code; none allocates, frees, synchronises or reads device memory on the host,
+ * so all of them are legal inside a CUDA stream capture, as the reference's
+ * decode and verify graphs require (src/model.cu:318-327,378-387).
+ *
+ * Element types.  The reference keeps activations AND the KV cache in fp32.
+ * This library keeps the cache in bf16 (same indexing: [pos][kv_head][dim], K
+ * and V in separate buffers, one such block per full-attention layer) and
+ * offers every launcher twice:
+ *   *_bf16  activations in bf16 -- the measured path;
+ *   *_f32   activations in fp32 exactly as the reference call sites hold them,
+ *           converted inside the kernels; only the cache element type differs.
+ * bf16 values cross this ABI as raw 16-bit patterns (uint16_t).
+ *
+ * Geometry supported: head_dim 256, rotary_dim 64, q_heads = 6 * kv_heads,
+ * kv_heads in {1, 2, 4} (4 is the model; 1 and 2 are the per-GPU slices of a
+ * KV-head-sharded layer).  Anything else returns QW_ERR_SHAPE.
+ */
+#ifndef QWENGINE_ATTN_H_
+#define QWENGINE_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint16_t qw_bf16;  /* raw bfloat16 bits                                   */
+typedef void *qw_stream;   /* a cudaStream_t                                      */
+
+enum {
+  QW_OK = 0,
+  QW_ERR_ARG = 1,       /* null pointer, negative count, misaligned buffer        */
+  QW_ERR_SHAPE = 2,     /* geometry outside the supported set                     */
+  QW_ERR_CUDA = 3,      /* a CUDA runtime / driver call failed                    */
+  QW_ERR_WORKSPACE = 4, /* scratch / workspace too small                          */
+  QW_ERR_DEVICE = 5     /* a kernel recorded an error (bounded wait ran out)      */
+};
+
+/* Human-readable text for a QW_ERR_* code. */
+const char *qw_strerror(int code);
+/* ABI version: bumped when a signature in this file changes. */
+int qw_abi_version(void);
+/* Last CUDA error string seen by this library on the calling thread ("" if none). */
+const char *qw_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Per-kernel launchers (drop-in for the reference's inline launches)
+ * ---------------------------------------------------------------------------------------- */
+
+/* Partial RoPE in place on v[B][heads][dim]; pairs (i, i+rot/2), angle
+ * (*dpos + b) * theta^(-2i/rot), or mpos[b*3 + component(i)] when mpos != NULL.
+ * Replaces rope(): src/elem.cu:255-259 (kernel k_rope, src/elem.cu:119-137);
+ * called at src/model.cu:228-229, src/prefill.cu:142-143, src/mtp.cu:172-173. */
+int qw_rope_bf16(qw_bf16 *v, int heads, int dim, int rot, const int *dpos, float theta,
+                 qw_stream stream, int B, const int *mpos);
+int qw_rope_f32(float *v, int heads, int dim, int rot, const int *dpos, float theta,
+                qw_stream stream, int B, const int *mpos);
+
+/* Store rows k[b], v[b] (kvdim elements each) at cache slot *dpos + b.
+ * Replaces k_kv_append<<<dim3(ceil(kvdim/256), B), 256>>>: src/mixers.cu:416-425;
+ * launched at src/model.cu:234, src/prefill.cu:148, src/mtp.cu:174. */
+int qw_kv_append_bf16(const qw_bf16 *k, const qw_bf16 *v, qw_bf16 *kc, qw_bf16 *vc,
+                      const int *dpos, int kvdim, int B, qw_stream stream);
+int qw_kv_append_f32(const float *k, const float *v, qw_bf16 *kc, qw_bf16 *vc,
+                     const int *dpos, int kvdim, int B, qw_stream stream);
+
+/* Decode / speculative-verify attention: row b of q[B][q_heads][dim] attends to the
+ * first *dpos + b + 1 cache rows (its own included).  `scratch` is the reference's
+ * score workspace (B * q_heads * ctx floats); here it holds split-KV partials and
+ * must be at least qw_attn_decode_scratch_floats() floats, which never exceeds the
+ * reference's size for ctx >= 512.  ctx is the number of rows in kc / vc.  1 <= B <= 8.
+ * Replaces k_attn_decode<<<dim3(q_heads, B), 256>>>: src/mixers.cu:436-525;
+ * launched at src/model.cu:236-238, src/mtp.cu:176-178. */
+int qw_attn_decode_bf16(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out,
+                        const int *dpos, int dim, int kv_heads, int q_heads, float scale,
+                        float *scratch, int ctx, int B, qw_stream stream);
+int qw_attn_decode_f32(const float *q, const qw_bf16 *kc, const qw_bf16 *vc, float *out,
+                       const int *dpos, int dim, int kv_heads, int q_heads, float scale,
+                       float *scratch, int ctx, int B, qw_stream stream);
+size_t qw_attn_decode_scratch_floats(int q_heads, int kv_heads, int ctx, int B);
+
+/* Chunked-prefill attention: row t of q[T][q_heads][dim] attends to the first
+ * *dpos + t + 1 cache rows.  `scratch` (reference: T * q_heads * ctx floats) is used
+ * only by the fallback kernel; qw_attn_prefill_scratch_floats() gives the minimum.
+ * Replaces k_attn_prefill<<<dim3(q_heads, ceil(T/8)), 256>>>: src/mixers.cu:546-649;
+ * launched at src/prefill.cu:152-154. */
+int qw_attn_prefill_bf16(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out,
+                         const int *dpos, int dim, int kv_heads, int q_heads, float scale,
+                         float *scratch, int ctx, int T, qw_stream stream);
+int qw_attn_prefill_f32(const float *q, const qw_bf16 *kc, const qw_bf16 *vc, float *out,
+                        const int *dpos, int dim, int kv_heads, int q_heads, float scale,
+                        float *scratch, int ctx, int T, qw_stream stream);
+size_t qw_attn_prefill_scratch_floats(int q_heads, int kv_heads, int ctx, int T);
+
+/* x[i] *= sigmoid(gate[i]) for i < n.
+ * Replaces k_gate_sigmoid<<<ceil(n/256), 256>>>: src/mixers.cu:653-657;
+ * launched at src/model.cu:239-240, src/prefill.cu:155-156, src/mtp.cu:179. */
+int qw_gate_sigmoid_bf16(qw_bf16 *x, const qw_bf16 *gate, int n, qw_stream stream);
+int qw_gate_sigmoid_f32(float *x, const float *gate, int n, qw_stream stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused, batched mixer (the measured path)
+ *
+ * One call = rope(q), rope(k), append, attention and the sigmoid gate for a batch of
+ * independent sequences -- the five launches of src/model.cu:228-240 (decode/verify),
+ * src/prefill.cu:142-156 (prefill chunk) and src/mtp.cu:172-179 (draft head) in one
+ * descriptor.  The reference serves one sequence; n_seq > 1 is a batched superset.
+ * ---------------------------------------------------------------------------------------- */
+
+enum {
+  QW_F_ROPE = 1,       /* rotate q and k_new (else they arrive rotated)                 */
+  QW_F_APPEND = 2,     /* write k_new / v_new into the cache before attending           */
+  QW_F_GATE = 4,       /* multiply the output by sigmoid(gate)                          */
+  QW_F_OUT_F32 = 8,    /* `out` is float instead of bf16 (checking aid)                 */
+  QW_F_NO_UMMA = 16    /* force the split-KV kernel even for long prefill chunks        */
+};
+
+typedef struct qw_mixer_desc {
+  /* geometry */
+  int n_seq;       /* sequences in this call                                            */
+  int n_new;       /* new tokens per sequence: 1 decode, 2..8 verify, up to 32768 prefill */
+  int q_heads, kv_heads, head_dim, rotary_dim;
+  float theta;     /* RoPE base (1e7)                                                   */
+  float scale;     /* softmax scale (1/16)                                              */
+  int flags;       /* QW_F_*                                                            */
+  /* activations, bf16, contiguous */
+  const qw_bf16 *q;     /* [n_seq][n_new][q_heads][head_dim]                            */
+  const qw_bf16 *k_new; /* [n_seq][n_new][kv_heads][head_dim]   (QW_F_APPEND)           */
+  const qw_bf16 *v_new; /* same shape                            (QW_F_APPEND)           */
+  const qw_bf16 *gate;  /* same shape as q                       (QW_F_GATE)             */
+  void *out;            /* same shape as q, bf16 (float with QW_F_OUT_F32)               */
+  float *lse;           /* [n_seq][n_new][q_heads] natural-log LSE, or NULL              */
+  /* cache pool: rows of kv_heads*head_dim bf16; sequence s owns rows
+   * cache_row[s] .. cache_row[s] + pos[s] + n_new - 1 */
+  qw_bf16 *kc, *vc;
+  int64_t cache_rows;        /* rows in the pool (extent of the tensor maps)            */
+  const int64_t *cache_row;  /* device, [n_seq]; NULL means all zero (one sequence)      */
+  const int *pos;            /* device, [n_seq]: tokens cached before this call (*dpos)  */
+  const int *mpos;           /* device, [n_seq][n_new][3] mrope positions, or NULL       */
+  /* workspace, device, qw_mixer_workspace_bytes() bytes, 256-byte aligned */
+  void *workspace;
+  size_t workspace_bytes;
+  /* device int that receives a non-zero code if a kernel gave up on a bounded wait; may
+   * be NULL.  It is only ever written on error. */
+  int *status;
+} qw_mixer_desc;
+
+size_t qw_mixer_workspace_bytes(const qw_mixer_desc *d);
+int qw_mixer_forward(const qw_mixer_desc *d, qw_stream stream);
+
+/* Number of kernels the last qw_* call on this thread launched (for launch accounting). */
+int qw_last_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Cross-GPU split-KV combine (used only where one sequence's KV range is split across GPUs)
+ *
+ * A partial is, per (row, q_head), QW_PARTIAL_FLOATS floats: o[256] un-normalised fp32,
+ * m (running max of scale*log2(e)*score) and l (sum of exp2), then two pad floats.
+ * qw_mixer_forward_partial() runs the mixer but emits partials [n_seq*n_new][q_heads][260]
+ * instead of normalised output; after the ranks exchange them (NCCL, outside this library)
+ * qw_combine_partials() merges n_parts of them, laid out [n_parts][rows][q_heads][260], in
+ * index order (fixed order => bit-stable) and applies the gate (QW_F_GATE, QW_F_OUT_F32).
+ * No counterpart in the reference (single GPU).
+ * ---------------------------------------------------------------------------------------- */
+#define QW_PARTIAL_FLOATS 260
+int qw_mixer_forward_partial(const qw_mixer_desc *d, float *partial, qw_stream stream);
+int qw_combine_partials(const float *parts, int n_parts, int64_t rows, int q_heads,
+                        const qw_bf16 *gate, void *out, float *lse, int flags, qw_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QWENGINE_ATTN_H_ */

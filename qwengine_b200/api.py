@@ -1,0 +1,193 @@
+"""ctypes binding of libqwengine_attn.so plus thin torch conveniences.
+
+The functions mirror the reference engine's launch sites by name and argument order
+(rope, kv_append, attn_decode, attn_prefill, gate_sigmoid: reference src/elem.cu:255,
+src/mixers.cu:416/436/546/653) and add the fused batched mixer.  torch is used only to
+hold device memory and streams; every computation happens inside the CUDA library, and
+there is no fallback: a missing or unloadable library raises.
+"""
+import ctypes as C
+import os
+
+import torch
+
+from . import build as _build
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libqwengine_attn.so")
+
+QW_OK = 0
+F_ROPE, F_APPEND, F_GATE, F_OUT_F32, F_NO_UMMA = 1, 2, 4, 8, 16
+PARTIAL_FLOATS = 260
+HEAD_DIM, ROTARY_DIM, GROUP = 256, 64, 6
+
+_vp, _i, _f = C.c_void_p, C.c_int, C.c_float
+
+
+class MixerDesc(C.Structure):
+    _fields_ = [
+        ("n_seq", _i), ("n_new", _i), ("q_heads", _i), ("kv_heads", _i), ("head_dim", _i),
+        ("rotary_dim", _i), ("theta", _f), ("scale", _f), ("flags", _i),
+        ("q", _vp), ("k_new", _vp), ("v_new", _vp), ("gate", _vp), ("out", _vp), ("lse", _vp),
+        ("kc", _vp), ("vc", _vp), ("cache_rows", C.c_int64), ("cache_row", _vp), ("pos", _vp),
+        ("mpos", _vp), ("workspace", _vp), ("workspace_bytes", C.c_size_t), ("status", _vp),
+    ]
+
+
+# name -> (restype, argtypes); the list doubles as the symbol inventory checked by the tests.
+_SIGS = {
+    "qw_strerror": (C.c_char_p, [_i]),
+    "qw_abi_version": (_i, []),
+    "qw_last_cuda_error": (C.c_char_p, []),
+    "qw_last_launch_count": (_i, []),
+    "qw_rope_bf16": (_i, [_vp, _i, _i, _i, _vp, _f, _vp, _i, _vp]),
+    "qw_rope_f32": (_i, [_vp, _i, _i, _i, _vp, _f, _vp, _i, _vp]),
+    "qw_kv_append_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "qw_kv_append_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "qw_attn_decode_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp]),
+    "qw_attn_decode_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp]),
+    "qw_attn_decode_scratch_floats": (C.c_size_t, [_i, _i, _i, _i]),
+    "qw_attn_prefill_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp]),
+    "qw_attn_prefill_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp]),
+    "qw_attn_prefill_scratch_floats": (C.c_size_t, [_i, _i, _i, _i]),
+    "qw_gate_sigmoid_bf16": (_i, [_vp, _vp, _i, _vp]),
+    "qw_gate_sigmoid_f32": (_i, [_vp, _vp, _i, _vp]),
+    "qw_mixer_workspace_bytes": (C.c_size_t, [C.POINTER(MixerDesc)]),
+    "qw_mixer_forward": (_i, [C.POINTER(MixerDesc), _vp]),
+    "qw_mixer_forward_partial": (_i, [C.POINTER(MixerDesc), _vp, _vp]),
+    "qw_combine_partials": (_i, [_vp, _i, C.c_int64, _i, _vp, _vp, _vp, _i, _vp]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded C-ABI library.  Builds it when nvcc is available and it is stale; raises if
+    it can be neither found nor built -- there is deliberately no other implementation."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            _build.build()
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(l, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = l
+    return _lib
+
+
+class QwError(RuntimeError):
+    pass
+
+
+def _check(rc):
+    if rc != QW_OK:
+        l = lib()
+        raise QwError("%s [%s]" % (l.qw_strerror(rc).decode(), l.qw_last_cuda_error().decode()))
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(stream=None):
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def _suffix(t):
+    if t.dtype == torch.bfloat16:
+        return "bf16"
+    if t.dtype == torch.float32:
+        return "f32"
+    raise TypeError("activations must be bfloat16 or float32")
+
+
+# ---- per-kernel launchers, named and ordered like the reference's --------------------------------
+def rope(v, heads, dim, rot, dpos, theta, stream=None, B=1, mpos=None):
+    _check(getattr(lib(), "qw_rope_" + _suffix(v))(_p(v), heads, dim, rot, _p(dpos), theta, _stream(stream), B, _p(mpos)))
+
+
+def kv_append(k, v, kc, vc, dpos, kvdim, B=1, stream=None):
+    _check(getattr(lib(), "qw_kv_append_" + _suffix(k))(_p(k), _p(v), _p(kc), _p(vc), _p(dpos), kvdim, B, _stream(stream)))
+
+
+def attn_decode(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, scratch, ctx, B=1, stream=None):
+    _check(getattr(lib(), "qw_attn_decode_" + _suffix(q))(
+        _p(q), _p(kc), _p(vc), _p(out), _p(dpos), dim, kv_heads, q_heads, scale, _p(scratch), ctx, B, _stream(stream)))
+
+
+def attn_prefill(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, scratch, ctx, T, stream=None):
+    _check(getattr(lib(), "qw_attn_prefill_" + _suffix(q))(
+        _p(q), _p(kc), _p(vc), _p(out), _p(dpos), dim, kv_heads, q_heads, scale, _p(scratch), ctx, T, _stream(stream)))
+
+
+def gate_sigmoid(x, gate, n, stream=None):
+    _check(getattr(lib(), "qw_gate_sigmoid_" + _suffix(x))(_p(x), _p(gate), n, _stream(stream)))
+
+
+def attn_decode_scratch_floats(q_heads, kv_heads, ctx, B):
+    return lib().qw_attn_decode_scratch_floats(q_heads, kv_heads, ctx, B)
+
+
+def attn_prefill_scratch_floats(q_heads, kv_heads, ctx, T):
+    return lib().qw_attn_prefill_scratch_floats(q_heads, kv_heads, ctx, T)
+
+
+# ---- fused batched mixer ------------------------------------------------------------------------------
+class Mixer:
+    """Holds the descriptor and workspace of one fused-mixer call shape so that repeated calls
+    (a decode loop, a benchmark) do no host allocation.  Tensors are bf16 on one CUDA device."""
+
+    def __init__(self, n_seq, n_new, kv_heads=4, theta=1e7, scale=1.0 / 16.0, device="cuda"):
+        self.n_seq, self.n_new, self.kv_heads, self.q_heads = n_seq, n_new, kv_heads, GROUP * kv_heads
+        d = MixerDesc()
+        d.n_seq, d.n_new, d.q_heads, d.kv_heads = n_seq, n_new, self.q_heads, kv_heads
+        d.head_dim, d.rotary_dim, d.theta, d.scale = HEAD_DIM, ROTARY_DIM, theta, scale
+        self.desc = d
+        nbytes = lib().qw_mixer_workspace_bytes(C.byref(d))
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        d.workspace, d.workspace_bytes, d.status = self.workspace.data_ptr(), nbytes, self.status.data_ptr()
+        self._keep = None
+
+    def bind(self, q, kc, vc, pos, out, k_new=None, v_new=None, gate=None, lse=None, cache_row=None,
+             mpos=None, flags=F_ROPE | F_APPEND | F_GATE):
+        d = self.desc
+        if out.dtype == torch.float32:
+            flags |= F_OUT_F32
+        if gate is None:
+            flags &= ~F_GATE
+        if k_new is None:
+            flags &= ~F_APPEND
+        d.flags = flags
+        d.q, d.k_new, d.v_new, d.gate = q.data_ptr(), _addr(k_new), _addr(v_new), _addr(gate)
+        d.out, d.lse, d.kc, d.vc = out.data_ptr(), _addr(lse), kc.data_ptr(), vc.data_ptr()
+        d.cache_rows = kc.numel() // (self.kv_heads * HEAD_DIM)
+        d.cache_row, d.pos, d.mpos = _addr(cache_row), pos.data_ptr(), _addr(mpos)
+        self._keep = (q, kc, vc, pos, out, k_new, v_new, gate, lse, cache_row, mpos)
+        return self
+
+    def forward(self, stream=None):
+        _check(lib().qw_mixer_forward(C.byref(self.desc), _stream(stream)))
+
+    def forward_partial(self, partial, stream=None):
+        _check(lib().qw_mixer_forward_partial(C.byref(self.desc), _p(partial), _stream(stream)))
+
+    def launches(self):
+        return lib().qw_last_launch_count()
+
+    def check_status(self):
+        code = int(self.status.item())
+        if code:
+            raise QwError("kernel reported device error code %d" % code)
+
+
+def _addr(t):
+    return None if t is None else t.data_ptr()
+
+
+def combine_partials(parts, n_parts, rows, q_heads, out, gate=None, lse=None, stream=None):
+    flags = (F_GATE if gate is not None else 0) | (F_OUT_F32 if out.dtype == torch.float32 else 0)
+    _check(lib().qw_combine_partials(_p(parts), n_parts, rows, q_heads, _p(gate), _p(out), _p(lse), flags,
+                                     _stream(stream)))

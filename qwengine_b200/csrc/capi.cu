@@ -1,0 +1,408 @@
+// extern "C" layer of the B200 full-attention mixer: argument checks, tensor-map
+// construction and kernel launches.  Nothing here allocates, frees or synchronises.
+#include "../../include/qwengine_attn.h"
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "elementwise.cuh"
+#include "prefill_umma.cuh"
+#include "splitkv.cuh"
+
+using namespace qwb;
+
+namespace {
+
+thread_local char g_cuda_err[256] = "";
+thread_local int g_launches = 0;
+
+int cuda_fail(cudaError_t e, const char *what) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+  return QW_ERR_CUDA;
+}
+#define QW_CUDA(x)                                  \
+  do {                                              \
+    cudaError_t e_ = (x);                           \
+    if (e_ != cudaSuccess) return cuda_fail(e_, #x); \
+  } while (0)
+
+int check_launch(const char *what) {
+  ++g_launches;
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? QW_OK : cuda_fail(e, what);
+}
+
+bool geometry_ok(int dim, int kv_heads, int q_heads) {
+  return dim == HEAD_DIM && (kv_heads == 1 || kv_heads == 2 || kv_heads == 4) && q_heads == GROUP * kv_heads;
+}
+
+RopeTable make_rope_table(float theta, int rot) {
+  RopeTable t;
+  for (int i = 0; i < ROT_PAIRS; ++i) t.inv_freq[i] = pow((double)theta, -2.0 * (double)i / (double)rot);
+  return t;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// cuTensorMapEncodeTiled through the runtime's entry-point lookup: no link-time libcuda.
+typedef CUresult (*encode_fn_t)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+encode_fn_t encode_fn() {
+  static encode_fn_t fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<encode_fn_t>(p);
+  });
+  return fn;
+}
+
+// Map over a bf16 matrix [rows][width] (row-major, width*2 bytes per row); box = 64 elements
+// (128 bytes, the swizzle span) x box_rows rows.  Out-of-range rows read as zero.
+int make_rowmajor_map(CUtensorMap *map, const void *base, int64_t rows, int width, int box_rows) {
+  encode_fn_t fn = encode_fn();
+  if (!fn) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not found");
+    return QW_ERR_CUDA;
+  }
+  if (reinterpret_cast<uintptr_t>(base) & 15) return QW_ERR_ARG;
+  const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return QW_ERR_CUDA;
+  }
+  return QW_OK;
+}
+
+// ---- split-KV launch ------------------------------------------------------------------------
+struct AttnCall {
+  const void *q;
+  bool q_is_f32;
+  const uint16_t *gate;
+  void *out;
+  bool out_is_f32;
+  float *lse;
+  float *partial_out;
+  const uint16_t *kc, *vc;
+  int64_t cache_rows;
+  const int64_t *cache_row;
+  const int *pos;
+  const int *mpos;
+  int n_seq, n_new, q_heads, kv_heads;
+  float theta, scale;
+  bool do_rope, do_gate;
+  float *ws;
+  size_t ws_floats;
+  int *status;
+};
+
+int splitkv_rb(int n_new) { return n_new < 5 ? n_new : 5; }  // tokens per unit: <= 30 rows = two 16-row tiles
+size_t splitkv_slot_floats(int rb) { return (size_t)rb * GROUP * PART_STRIDE; }
+
+template <int MT, int DS, int STAGES, typename TIn, typename TOut>
+int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, cudaStream_t st) {
+  auto kern = splitkv_kernel<MT, DS, STAGES, TIn, TOut>;
+  constexpr size_t smem = splitkv_smem_bytes<MT, DS, STAGES>();
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    QW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = true;
+  }
+  kern<<<p.G, (SK_KS * DS + 1) * 32, smem, st>>>(mk, mv, p);
+  int rc = check_launch("splitkv_kernel");
+  if (rc) return rc;
+  const int n_units = p.n_seq * p.nblk * p.kv_heads;
+  splitkv_merge_kernel<TOut><<<n_units, 256, 0, st>>>(p);
+  return check_launch("splitkv_merge_kernel");
+}
+
+int launch_splitkv(const AttnCall &c, cudaStream_t st) {
+  SplitKVParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = c.q; p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.partial_out = c.partial_out;
+  p.pos = c.pos; p.cache_row = c.cache_row; p.mpos = c.mpos; p.ws = c.ws; p.status = c.status;
+  p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
+  p.rb = splitkv_rb(c.n_new);
+  p.nblk = (c.n_new + p.rb - 1) / p.rb;
+  const long long n_units = (long long)c.n_seq * p.nblk * c.kv_heads;
+  if (n_units > (1 << 24)) return QW_ERR_SHAPE;
+  const size_t slot = splitkv_slot_floats(p.rb);
+  const long long max_slots = (long long)(c.ws_floats / slot);
+  long long G = sm_count();
+  if (max_slots - n_units < G) G = max_slots - n_units;
+  if (G < 1) return QW_ERR_WORKSPACE;
+  p.G = (int)G;
+  p.q_lo_dims = c.q_is_f32 ? HEAD_DIM : (c.do_rope ? ROTARY_DIM : 0);
+  p.scale_log2 = c.scale * LOG2E;
+  p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate;
+  p.rope = make_rope_table(c.theta, ROTARY_DIM);
+
+  CUtensorMap mk, mv;
+  int rc = make_rowmajor_map(&mk, c.kc, c.cache_rows, c.kv_heads * HEAD_DIM, SK_TK);
+  if (rc) return rc;
+  rc = make_rowmajor_map(&mv, c.vc, c.cache_rows, c.kv_heads * HEAD_DIM, SK_TK);
+  if (rc) return rc;
+
+  const int mt = (p.rb * GROUP + 15) / 16;
+  if (mt == 1) {
+    if (c.q_is_f32) return launch_splitkv_t<1, 2, 3, float, float>(mk, mv, p, st);
+    if (c.out_is_f32) return launch_splitkv_t<1, 2, 3, uint16_t, float>(mk, mv, p, st);
+    return launch_splitkv_t<1, 2, 3, uint16_t, uint16_t>(mk, mv, p, st);
+  }
+  if (c.q_is_f32) return launch_splitkv_t<2, 2, 3, float, float>(mk, mv, p, st);
+  if (c.out_is_f32) return launch_splitkv_t<2, 2, 3, uint16_t, float>(mk, mv, p, st);
+  return launch_splitkv_t<2, 2, 3, uint16_t, uint16_t>(mk, mv, p, st);
+}
+
+size_t splitkv_ws_floats(int n_seq, int n_new, int kv_heads) {
+  const int rb = splitkv_rb(n_new);
+  const long long nblk = (n_new + rb - 1) / rb;
+  const long long n_units = (long long)n_seq * nblk * kv_heads;
+  return (size_t)(sm_count() + n_units) * splitkv_slot_floats(rb);
+}
+
+bool desc_ok(const qw_mixer_desc *d) {
+  if (!d || d->n_seq < 0 || d->n_new < 0) return false;
+  if (!d->q || !d->out || !d->kc || !d->vc || !d->pos || d->cache_rows <= 0) return false;
+  if ((d->flags & QW_F_APPEND) && (!d->k_new || !d->v_new)) return false;
+  if ((d->flags & QW_F_GATE) && !d->gate) return false;
+  return true;
+}
+
+int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) {
+  g_launches = 0;
+  if (!desc_ok(d)) return QW_ERR_ARG;
+  if (!geometry_ok(d->head_dim, d->kv_heads, d->q_heads) || d->rotary_dim != ROTARY_DIM) return QW_ERR_SHAPE;
+  if (d->n_seq == 0 || d->n_new == 0) return QW_OK;
+  if ((long long)d->n_seq * d->n_new > (1ll << 30)) return QW_ERR_SHAPE;
+  const RopeTable tab = make_rope_table(d->theta, ROTARY_DIM);
+  if (d->flags & QW_F_APPEND) {
+    rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
+        d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
+        (d->flags & QW_F_ROPE) ? 1 : 0, tab);
+    int rc = check_launch("rope_append_kernel");
+    if (rc) return rc;
+  }
+  const bool use_umma = !(d->flags & QW_F_NO_UMMA) && !partial && prefill_umma_supported(d->n_new);
+  if (use_umma) {
+    PrefillCall pc;
+    memset(&pc, 0, sizeof(pc));
+    pc.q = d->q; pc.gate = (d->flags & QW_F_GATE) ? d->gate : nullptr; pc.out = d->out;
+    pc.out_is_f32 = (d->flags & QW_F_OUT_F32) != 0; pc.lse = d->lse;
+    pc.kc = d->kc; pc.vc = d->vc; pc.cache_rows = d->cache_rows; pc.cache_row = d->cache_row;
+    pc.pos = d->pos; pc.mpos = d->mpos; pc.n_seq = d->n_seq; pc.n_new = d->n_new;
+    pc.q_heads = d->q_heads; pc.kv_heads = d->kv_heads; pc.scale = d->scale;
+    pc.do_rope = (d->flags & QW_F_ROPE) != 0; pc.status = d->status;
+    pc.rope = tab;
+    int n = 0;
+    int rc = launch_prefill_umma(pc, st, &n);
+    g_launches += n;
+    if (rc == QW_ERR_CUDA) {
+      cudaError_t e = cudaGetLastError();
+      return cuda_fail(e, "prefill_umma_kernel");
+    }
+    return rc;
+  }
+  AttnCall c;
+  memset(&c, 0, sizeof(c));
+  c.q = d->q; c.q_is_f32 = false; c.gate = d->gate; c.out = d->out;
+  c.out_is_f32 = (d->flags & QW_F_OUT_F32) != 0; c.lse = d->lse; c.partial_out = partial;
+  c.kc = d->kc; c.vc = d->vc; c.cache_rows = d->cache_rows; c.cache_row = d->cache_row;
+  c.pos = d->pos; c.mpos = d->mpos; c.n_seq = d->n_seq; c.n_new = d->n_new;
+  c.q_heads = d->q_heads; c.kv_heads = d->kv_heads; c.theta = d->theta; c.scale = d->scale;
+  c.do_rope = (d->flags & QW_F_ROPE) != 0; c.do_gate = (d->flags & QW_F_GATE) != 0;
+  c.ws = reinterpret_cast<float *>(d->workspace); c.ws_floats = d->workspace_bytes / sizeof(float);
+  c.status = d->status;
+  if (!c.ws || (reinterpret_cast<uintptr_t>(c.ws) & 15)) return QW_ERR_WORKSPACE;
+  return launch_splitkv(c, st);
+}
+
+// Drop-in attention launchers share this: one sequence, rows already rotated and appended.
+template <typename T>
+int attn_dropin(const T *q, const qw_bf16 *kc, const qw_bf16 *vc, T *out, const int *dpos, int dim, int kv_heads,
+                int q_heads, float scale, float *scratch, int ctx, int rows, bool decode, cudaStream_t st) {
+  g_launches = 0;
+  if (!q || !kc || !vc || !out || !dpos || !scratch || ctx <= 0 || rows < 0) return QW_ERR_ARG;
+  if (!geometry_ok(dim, kv_heads, q_heads)) return QW_ERR_SHAPE;
+  if (decode && rows > 8) return QW_ERR_SHAPE;
+  if (rows == 0) return QW_OK;
+  AttnCall c;
+  memset(&c, 0, sizeof(c));
+  c.q = q; c.q_is_f32 = sizeof(T) == 4; c.out = out; c.out_is_f32 = sizeof(T) == 4;
+  c.kc = kc; c.vc = vc; c.cache_rows = ctx; c.pos = dpos;
+  c.n_seq = 1; c.n_new = rows; c.q_heads = q_heads; c.kv_heads = kv_heads;
+  c.theta = 1e7f; c.scale = scale; c.ws = scratch;
+  c.ws_floats = decode ? (size_t)rows * q_heads * ctx : qw_attn_prefill_scratch_floats(q_heads, kv_heads, ctx, rows);
+  return launch_splitkv(c, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *qw_strerror(int code) {
+  switch (code) {
+    case QW_OK: return "ok";
+    case QW_ERR_ARG: return "bad argument (null pointer, negative count or misaligned buffer)";
+    case QW_ERR_SHAPE: return "unsupported geometry (need head_dim 256, rotary 64, q_heads = 6 * kv_heads, kv_heads 1/2/4)";
+    case QW_ERR_CUDA: return "a CUDA call failed (see qw_last_cuda_error)";
+    case QW_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case QW_ERR_DEVICE: return "a kernel reported an error through the status word";
+    default: return "unknown error code";
+  }
+}
+int qw_abi_version(void) { return 1; }
+const char *qw_last_cuda_error(void) { return g_cuda_err; }
+int qw_last_launch_count(void) { return g_launches; }
+
+int qw_rope_bf16(qw_bf16 *v, int heads, int dim, int rot, const int *dpos, float theta, qw_stream stream, int B,
+                 const int *mpos) {
+  g_launches = 0;
+  if (!v || !dpos || heads <= 0 || B < 0) return QW_ERR_ARG;
+  if (dim != HEAD_DIM || rot != ROTARY_DIM) return QW_ERR_SHAPE;
+  if (B == 0) return QW_OK;
+  rope_inplace_kernel<uint16_t><<<dim3(heads, B), 32, 0, (cudaStream_t)stream>>>(v, heads, dpos, mpos,
+                                                                                 make_rope_table(theta, rot));
+  return check_launch("rope_inplace_kernel");
+}
+int qw_rope_f32(float *v, int heads, int dim, int rot, const int *dpos, float theta, qw_stream stream, int B,
+                const int *mpos) {
+  g_launches = 0;
+  if (!v || !dpos || heads <= 0 || B < 0) return QW_ERR_ARG;
+  if (dim != HEAD_DIM || rot != ROTARY_DIM) return QW_ERR_SHAPE;
+  if (B == 0) return QW_OK;
+  rope_inplace_kernel<float><<<dim3(heads, B), 32, 0, (cudaStream_t)stream>>>(v, heads, dpos, mpos,
+                                                                              make_rope_table(theta, rot));
+  return check_launch("rope_inplace_kernel");
+}
+
+int qw_kv_append_bf16(const qw_bf16 *k, const qw_bf16 *v, qw_bf16 *kc, qw_bf16 *vc, const int *dpos, int kvdim,
+                      int B, qw_stream stream) {
+  g_launches = 0;
+  if (!k || !v || !kc || !vc || !dpos || kvdim <= 0 || B < 0) return QW_ERR_ARG;
+  if (kvdim % 8) return QW_ERR_SHAPE;
+  if (B == 0) return QW_OK;
+  kv_append_kernel<uint16_t><<<dim3((kvdim + 2047) / 2048, B), 256, 0, (cudaStream_t)stream>>>(k, v, kc, vc, dpos,
+                                                                                              kvdim);
+  return check_launch("kv_append_kernel");
+}
+int qw_kv_append_f32(const float *k, const float *v, qw_bf16 *kc, qw_bf16 *vc, const int *dpos, int kvdim, int B,
+                     qw_stream stream) {
+  g_launches = 0;
+  if (!k || !v || !kc || !vc || !dpos || kvdim <= 0 || B < 0) return QW_ERR_ARG;
+  if (kvdim % 8) return QW_ERR_SHAPE;
+  if (B == 0) return QW_OK;
+  kv_append_kernel<float><<<dim3((kvdim + 2047) / 2048, B), 256, 0, (cudaStream_t)stream>>>(k, v, kc, vc, dpos,
+                                                                                           kvdim);
+  return check_launch("kv_append_kernel");
+}
+
+int qw_gate_sigmoid_bf16(qw_bf16 *x, const qw_bf16 *gate, int n, qw_stream stream) {
+  g_launches = 0;
+  if (!x || !gate || n < 0) return QW_ERR_ARG;
+  if (n % 8) return QW_ERR_SHAPE;
+  if (n == 0) return QW_OK;
+  gate_sigmoid_kernel<uint16_t><<<(n / 8 + 255) / 256, 256, 0, (cudaStream_t)stream>>>(x, gate, n);
+  return check_launch("gate_sigmoid_kernel");
+}
+int qw_gate_sigmoid_f32(float *x, const float *gate, int n, qw_stream stream) {
+  g_launches = 0;
+  if (!x || !gate || n < 0) return QW_ERR_ARG;
+  if (n % 8) return QW_ERR_SHAPE;
+  if (n == 0) return QW_OK;
+  gate_sigmoid_kernel<float><<<(n / 8 + 255) / 256, 256, 0, (cudaStream_t)stream>>>(x, gate, n);
+  return check_launch("gate_sigmoid_kernel");
+}
+
+size_t qw_attn_decode_scratch_floats(int q_heads, int kv_heads, int ctx, int B) {
+  (void)q_heads; (void)ctx;
+  if (B <= 0 || kv_heads <= 0) return 0;
+  // one CTA slot plus one slot per unit is the minimum; more slots allow more CTAs
+  const int rb = splitkv_rb(B);
+  const int nblk = (B + rb - 1) / rb;
+  return (size_t)(1 + nblk * kv_heads) * splitkv_slot_floats(rb);
+}
+size_t qw_attn_prefill_scratch_floats(int q_heads, int kv_heads, int ctx, int T) {
+  (void)q_heads; (void)ctx;
+  if (T <= 0 || kv_heads <= 0) return 0;
+  return splitkv_ws_floats(1, T, kv_heads);
+}
+
+int qw_attn_decode_bf16(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out, const int *dpos,
+                        int dim, int kv_heads, int q_heads, float scale, float *scratch, int ctx, int B,
+                        qw_stream stream) {
+  return attn_dropin<qw_bf16>(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, scratch, ctx, B, true,
+                              (cudaStream_t)stream);
+}
+int qw_attn_decode_f32(const float *q, const qw_bf16 *kc, const qw_bf16 *vc, float *out, const int *dpos, int dim,
+                       int kv_heads, int q_heads, float scale, float *scratch, int ctx, int B, qw_stream stream) {
+  return attn_dropin<float>(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, scratch, ctx, B, true,
+                            (cudaStream_t)stream);
+}
+int qw_attn_prefill_bf16(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out, const int *dpos,
+                         int dim, int kv_heads, int q_heads, float scale, float *scratch, int ctx, int T,
+                         qw_stream stream) {
+  return attn_dropin<qw_bf16>(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, scratch, ctx, T, false,
+                              (cudaStream_t)stream);
+}
+int qw_attn_prefill_f32(const float *q, const qw_bf16 *kc, const qw_bf16 *vc, float *out, const int *dpos, int dim,
+                        int kv_heads, int q_heads, float scale, float *scratch, int ctx, int T, qw_stream stream) {
+  return attn_dropin<float>(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, scratch, ctx, T, false,
+                            (cudaStream_t)stream);
+}
+
+size_t qw_mixer_workspace_bytes(const qw_mixer_desc *d) {
+  if (!d || d->n_seq <= 0 || d->n_new <= 0 || d->kv_heads <= 0) return 256;
+  return splitkv_ws_floats(d->n_seq, d->n_new, d->kv_heads) * sizeof(float) + 256;
+}
+int qw_mixer_forward(const qw_mixer_desc *d, qw_stream stream) {
+  return mixer_forward_impl(d, nullptr, (cudaStream_t)stream);
+}
+int qw_mixer_forward_partial(const qw_mixer_desc *d, float *partial, qw_stream stream) {
+  if (!partial) return QW_ERR_ARG;
+  return mixer_forward_impl(d, partial, (cudaStream_t)stream);
+}
+
+int qw_combine_partials(const float *parts, int n_parts, int64_t rows, int q_heads, const qw_bf16 *gate, void *out,
+                        float *lse, int flags, qw_stream stream) {
+  g_launches = 0;
+  if (!parts || !out || n_parts <= 0 || rows < 0 || q_heads <= 0) return QW_ERR_ARG;
+  if ((flags & QW_F_GATE) && !gate) return QW_ERR_ARG;
+  if (rows == 0) return QW_OK;
+  const long long n = (long long)rows * q_heads;
+  const unsigned blocks = (unsigned)((n + 7) / 8);
+  if (flags & QW_F_OUT_F32)
+    combine_partials_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        parts, n_parts, n, (flags & QW_F_GATE) ? gate : nullptr, reinterpret_cast<float *>(out), lse);
+  else
+    combine_partials_kernel<uint16_t><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        parts, n_parts, n, (flags & QW_F_GATE) ? gate : nullptr, reinterpret_cast<uint16_t *>(out), lse);
+  return check_launch("combine_partials_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,94 @@
+// The small kernels around attention: stand-alone RoPE, KV append, sigmoid gate (the
+// reference's k_rope / k_kv_append / k_gate_sigmoid launch sites), and the fused
+// rope(k) + append used by the batched mixer.
+#pragma once
+
+#include "common.cuh"
+
+namespace qwb {
+
+// In-place partial RoPE on v[B][heads][256]; grid (heads, B), block 32 -- one thread per
+// rotary pair, the launch shape of the reference's rope() (src/elem.cu:255-259).
+template <typename T>
+__global__ void __launch_bounds__(32) rope_inplace_kernel(T *v, int heads, const int *dpos, const int *mpos,
+                                                          const __grid_constant__ RopeTable tab) {
+  const int h = blockIdx.x, b = blockIdx.y, i = threadIdx.x;
+  const int pos = mpos ? mpos[b * 3 + mrope_component(i)] : (*dpos + b);
+  T *p = v + ((size_t)b * heads + h) * HEAD_DIM;
+  double c, s;
+  rope_sincos_exact(pos, tab.inv_freq[i], c, s);
+  const double x = load_as_f32<T>(p + i), y = load_as_f32<T>(p + i + ROT_PAIRS);
+  store_from_f32<T>(p + i, (float)(x * c - y * s));
+  store_from_f32<T>(p + i + ROT_PAIRS, (float)(x * s + y * c));
+}
+
+// kc[(pos + b) * kvdim + i] = k[b * kvdim + i], same for V (reference src/mixers.cu:416-425),
+// cache in bf16.  grid (ceil(kvdim / 2048), B), block 256, 8 elements per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) kv_append_kernel(const T *k, const T *v, uint16_t *kc, uint16_t *vc,
+                                                        const int *dpos, int kvdim) {
+  const int i = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (i >= kvdim) return;
+  const int b = blockIdx.y;
+  const size_t dst = (size_t)(*dpos + b) * kvdim + i, src = (size_t)b * kvdim + i;
+  float x[8];
+  load8<T>(k + src, x);
+  store8<uint16_t>(kc + dst, x);
+  load8<T>(v + src, x);
+  store8<uint16_t>(vc + dst, x);
+}
+
+// x[i] *= sigmoid(gate[i]) (reference src/mixers.cu:653-657); 8 elements per thread, n % 8 == 0.
+template <typename T>
+__global__ void __launch_bounds__(256) gate_sigmoid_kernel(T *x, const T *gate, int n) {
+  const int i = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (i >= n) return;
+  float a[8], g[8];
+  load8<T>(x + i, a);
+  load8<T>(gate + i, g);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] *= sigmoidf_(g[j]);
+  store8<T>(x + i, a);
+}
+
+// Fused rope(k) + append for a batch: one block per new token row, kv_heads * 32 threads,
+// thread = one 8-channel group of one head.  The 32 (cos, sin) pairs of the row's position
+// are computed once in double and shared by all heads.
+__global__ void __launch_bounds__(128) rope_append_kernel(const uint16_t *k_new, const uint16_t *v_new, uint16_t *kc,
+                                                          uint16_t *vc, const int *pos, const int64_t *cache_row,
+                                                          const int *mpos, int n_new, int kv_heads, int do_rope,
+                                                          const __grid_constant__ RopeTable tab) {
+  __shared__ double cs[ROT_PAIRS][2];
+  const size_t r = blockIdx.x;  // flat row s * n_new + b
+  const int s = (int)(r / n_new), b = (int)(r % n_new);
+  const int pz = pos[s] + b;
+  if (do_rope && threadIdx.x < ROT_PAIRS) {
+    const int i = threadIdx.x;
+    const int pp = mpos ? mpos[r * 3 + mrope_component(i)] : pz;
+    rope_sincos_exact(pp, tab.inv_freq[i], cs[i][0], cs[i][1]);
+  }
+  __syncthreads();
+  const int h = threadIdx.x >> 5, c16 = threadIdx.x & 31;
+  if (h >= kv_heads) return;
+  const size_t src = (r * kv_heads + h) * HEAD_DIM + c16 * 8;
+  const size_t dst = ((size_t)((cache_row ? cache_row[s] : 0) + pz) * kv_heads + h) * HEAD_DIM + c16 * 8;
+  *reinterpret_cast<uint4 *>(vc + dst) = *reinterpret_cast<const uint4 *>(v_new + src);
+  if (!do_rope || c16 >= 8) {
+    *reinterpret_cast<uint4 *>(kc + dst) = *reinterpret_cast<const uint4 *>(k_new + src);
+  } else if (c16 < 4) {
+    float x[8], y[8];
+    load8<uint16_t>(k_new + src, x);
+    load8<uint16_t>(k_new + src + ROT_PAIRS, y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const double c = cs[c16 * 8 + j][0], sn = cs[c16 * 8 + j][1];
+      const double xr = (double)x[j] * c - (double)y[j] * sn, yr = (double)x[j] * sn + (double)y[j] * c;
+      x[j] = (float)xr;
+      y[j] = (float)yr;
+    }
+    store8<uint16_t>(kc + dst, x);
+    store8<uint16_t>(kc + dst + ROT_PAIRS, y);
+  }
+}
+
+}  // namespace qwb

@@ -1,0 +1,31 @@
+// Causal chunked-prefill attention on tcgen05 / TMEM (interface; kernel in prefill_umma.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace qwb {
+
+struct PrefillCall {
+  const uint16_t *q;     // [n_seq][n_new][q_heads][256] bf16, un-rotated when do_rope
+  const uint16_t *gate;  // same shape or null
+  void *out;             // same shape, bf16 or fp32
+  bool out_is_f32;
+  float *lse;            // [n_seq][n_new][q_heads] or null
+  const uint16_t *kc, *vc;
+  int64_t cache_rows;
+  const int64_t *cache_row;
+  const int *pos;
+  const int *mpos;
+  int n_seq, n_new, q_heads, kv_heads;
+  float scale;
+  bool do_rope;
+  int *status;
+  RopeTable rope;
+};
+
+// True when the tcgen05 kernel takes a chunk of n_new rows (shorter chunks go to split-KV).
+bool prefill_umma_supported(int n_new);
+// Launches the kernel(s); *n_launched receives how many.  Returns a QW_* code.
+int launch_prefill_umma(const PrefillCall &c, cudaStream_t st, int *n_launched);
+
+}  // namespace qwb

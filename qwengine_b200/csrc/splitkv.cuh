@@ -1,0 +1,641 @@
+// Split-KV ("flash-decoding") attention for decode, speculative verify and short chunks.
+//
+// Work model.  A *unit* is one (sequence, block of <= 5 new tokens, KV head): its 6*tokens
+// query rows all read the same K/V rows.  The key range of every unit is cut into tiles of
+// 64 keys; all tiles of all units form one flat list that is divided evenly over the G CTAs
+// of a persistent grid, so ragged batches stay balanced and the grid never depends on a
+// length the host does not know (lengths live in device memory so the launch can be replayed
+// from a CUDA graph, as the reference's decode graph requires, src/model.cu:318-327).
+// A CTA walks its slice as 1..n *segments* (unit, tile range).  A segment that covers its
+// whole unit writes the final output; otherwise it writes an un-normalised partial
+// (o[256], m, l) to workspace slot (cta + unit), and a second small kernel merges the
+// partials of each unit in CTA order -- fixed order, no atomics, bit-stable run to run.
+//
+// Inside a CTA: one producer warp streams K and V tiles with TMA into a 128-byte-swizzled
+// shared-memory ring (HBM is the bound, so bytes in flight are what matter); 4*DS consumer
+// warps each own a 16-key slice of the tile (and 256/DS output channels) and run
+// QK^T -> online softmax -> PV on mma.sync m16n8k16 bf16 tensor-core tiles with fp32
+// accumulation.  Tensor cores are used because at 6 rows per KV head the CUDA-core FMA issue
+// time is already ~2/3 of the HBM time, and at 24 rows (4-token verify) 2.5x over it.
+// Q (after RoPE) and P are fed as bf16 hi + lo pairs so that neither is rounded to 8 bits.
+#pragma once
+
+#include "common.cuh"
+
+namespace qwb {
+
+constexpr int SK_TK = 64;                       // keys per tile
+constexpr int SK_TILE_BYTES = SK_TK * 512;      // one head's K (or V) tile: 64 keys x 256 bf16
+constexpr int SK_STAGE_BYTES = 2 * SK_TILE_BYTES;
+constexpr int SK_KS = SK_TK / 16;               // key slices (consumer warps along keys)
+
+struct SplitKVParams {
+  const void *q;          // [n_seq][n_new][q_heads][256]
+  const uint16_t *gate;   // same shape, bf16, or null
+  void *out;              // same shape
+  float *lse;             // [n_seq][n_new][q_heads] or null
+  float *partial_out;     // non-null: emit (o, m, l) per (row, head) instead of out / lse
+  const int *pos;         // [n_seq]
+  const int64_t *cache_row;  // [n_seq] or null
+  const int *mpos;        // [n_seq][n_new][3] or null
+  float *ws;              // (G + n_units) slots of rb*6*PART_STRIDE floats
+  int *status;
+  int n_seq, n_new, q_heads, kv_heads;
+  int rb;                 // tokens per unit block
+  int nblk;               // blocks per sequence
+  int G;                  // CTAs in the grid
+  int q_lo_dims;          // 0, 64 or 256: leading dims that carry a bf16 "lo" part
+  float scale_log2;       // softmax scale * log2(e)
+  int do_rope, do_gate;
+  RopeTable rope;
+};
+
+struct UnitInfo {
+  int s, blk, kvh;
+  int tok0, ntok;   // first new-token index of the block and tokens in it
+  int pos;          // tokens cached before the call for this sequence
+  int len;          // keys visible to the last row of the unit
+};
+
+__device__ __forceinline__ UnitInfo unit_info(const SplitKVParams &p, int u) {
+  UnitInfo ui;
+  ui.kvh = u % p.kv_heads;
+  const int sb = u / p.kv_heads;
+  ui.blk = sb % p.nblk;
+  ui.s = sb / p.nblk;
+  ui.tok0 = ui.blk * p.rb;
+  ui.ntok = min(p.rb, p.n_new - ui.tok0);
+  ui.pos = p.pos[ui.s];
+  ui.len = ui.pos + ui.tok0 + ui.ntok;
+  return ui;
+}
+__device__ __forceinline__ int unit_tiles(const SplitKVParams &p, int u) {
+  const UnitInfo ui = unit_info(p, u);
+  return (ui.len + SK_TK - 1) / SK_TK;
+}
+
+// Warp-cooperative: total number of tiles over all units.
+__device__ __forceinline__ long long warp_total_tiles(const SplitKVParams &p, int n_units, int lane) {
+  long long t = 0;
+  for (int u = lane; u < n_units; u += 32) t += unit_tiles(p, u);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+// Warp-cooperative: the unit containing flat tile g and the flat index of that unit's tile 0.
+__device__ __forceinline__ void warp_find_unit(const SplitKVParams &p, int n_units, int lane, long long g,
+                                               int &u_out, long long &pre_out) {
+  long long carry = 0;
+  u_out = n_units;
+  pre_out = 0;
+  for (int base = 0; base < n_units; base += 32) {
+    const int u = base + lane;
+    const long long mine = u < n_units ? unit_tiles(p, u) : 0;
+    long long inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const long long v = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += v;
+    }
+    const long long excl = carry + inc - mine;
+    const bool hit = u < n_units && mine > 0 && g >= excl && g < excl + mine;
+    const unsigned ball = __ballot_sync(0xffffffffu, hit);
+    if (ball) {
+      const int src = __ffs(ball) - 1;
+      u_out = base + src;
+      pre_out = __shfl_sync(0xffffffffu, excl, src);
+      return;
+    }
+    carry += __shfl_sync(0xffffffffu, inc, 31);
+  }
+}
+// Warp-cooperative: flat index of tile 0 of unit u.
+__device__ __forceinline__ long long warp_unit_prefix(const SplitKVParams &p, int u_target, int lane) {
+  long long t = 0;
+  for (int u = lane; u < u_target; u += 32) t += unit_tiles(p, u);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+// CTA that owns flat tile g when `total` tiles are cut into G slices [c*total/G, (c+1)*total/G).
+__device__ __forceinline__ int cta_of_tile(long long g, long long total, int G) {
+  return (int)(((g + 1) * (long long)G - 1) / total);
+}
+
+__device__ __forceinline__ void consumer_sync(int nthreads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+}
+
+// Offsets inside the Q staging area (also reused as the fp32 combine buffer).
+// q_hi: [MT*16 rows][256] bf16, 512-byte rows, 16-byte chunk index XORed with (row & 7).
+__device__ __forceinline__ uint32_t q_hi_off(int row, int d) {
+  const int c16 = d >> 3;
+  return (uint32_t)(row * 512 + ((c16 ^ (row & 7)) << 4) + ((d & 7) << 1));
+}
+
+template <int MT, int DS, int STAGES, typename TIn, typename TOut>
+__global__ void __launch_bounds__((SK_KS * DS + 1) * 32, 1)
+splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+               const __grid_constant__ SplitKVParams p) {
+  constexpr int NCW = SK_KS * DS;          // consumer warps
+  constexpr int NCT = NCW * 32;            // consumer threads
+  constexpr int ROWS = MT * 16;            // padded rows
+  constexpr int DW = HEAD_DIM / DS;        // output channels per warp
+  constexpr int NT_O = DW / 8;             // 8-wide output n-tiles per warp
+  constexpr int QREGION = ROWS * 1024;     // q_hi + q_lo (bf16) or combine buffer (fp32)
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t *stage_base = smem;
+  uint8_t *qregion = smem + STAGES * SK_STAGE_BYTES;
+  float *mx = reinterpret_cast<float *>(qregion + QREGION);  // [SK_KS][ROWS]
+  float *lx = mx + SK_KS * ROWS;                             // [SK_KS][ROWS]
+  uint64_t *full = reinterpret_cast<uint64_t *>(lx + SK_KS * ROWS);
+  uint64_t *empty = full + STAGES;
+  long long *seg = reinterpret_cast<long long *>(empty + STAGES);  // [0]=total [1]=pre(u_first) [2]=u_first
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_units = p.n_seq * p.nblk * p.kv_heads;
+  const int cta = blockIdx.x;
+
+  if (tid == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], NCW); }
+    fence_barrier_init();
+    prefetch_tensormap(&mapK);
+    prefetch_tensormap(&mapV);
+  }
+  if (warp == 0) {
+    const long long total = warp_total_tiles(p, n_units, lane);
+    const long long g0 = total * cta / p.G;
+    int u0; long long pre0;
+    warp_find_unit(p, n_units, lane, g0, u0, pre0);
+    if (lane == 0) { seg[0] = total; seg[1] = pre0; seg[2] = u0; }
+  }
+  __syncthreads();
+  const long long total = seg[0];
+  const long long g0 = total * cta / p.G, g1 = total * (cta + 1) / p.G;
+  if (g0 >= g1) return;  // uniform for the whole CTA
+
+  if (warp == NCW) {
+    // ---------------- producer: one lane streams the tiles of every segment ----------------
+    if (lane == 0) {
+      int u = (int)seg[2];
+      long long pre = seg[1];
+      uint32_t it = 0;
+      bool ok = true;
+      while (pre < g1 && u < n_units && ok) {
+        const UnitInfo ui = unit_info(p, u);
+        const int nt = (ui.len + SK_TK - 1) / SK_TK;
+        const int t0 = (int)(max(g0, pre) - pre), t1 = (int)(min(g1, pre + nt) - pre);
+        const long long row0 = p.cache_row ? p.cache_row[ui.s] : 0;
+        for (int t = t0; t < t1 && ok; ++t, ++it) {
+          const int st = it % STAGES;
+          if (it >= STAGES) {
+            if (!mbar_wait(&empty[st], ((it / STAGES) - 1) & 1)) {
+              if (p.status) *p.status = DEV_ERR_EMPTY_WAIT;
+              ok = false;
+              break;
+            }
+          }
+          uint8_t *kd = stage_base + st * SK_STAGE_BYTES, *vd = kd + SK_TILE_BYTES;
+          mbar_expect_tx(&full[st], SK_STAGE_BYTES);
+          const int r = (int)(row0 + (long long)t * SK_TK);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tma_load_2d(kd + c * (SK_TK * 128), &mapK, &full[st], ui.kvh * HEAD_DIM + c * 64, r);
+            tma_load_2d(vd + c * (SK_TK * 128), &mapV, &full[st], ui.kvh * HEAD_DIM + c * 64, r);
+          }
+        }
+        pre += nt;
+        ++u;
+      }
+    }
+    return;
+  }
+
+  // ---------------------------- consumers ---------------------------------------------------
+  const int ks = warp % SK_KS, ds = warp / SK_KS;
+  const int qd = lane >> 2, ql = lane & 3;  // row-in-8 and column pair of the mma fragments
+  bool ok = true;
+  uint32_t it = 0;
+  int u = (int)seg[2];
+  long long pre = seg[1];
+  const uint32_t qhi_s = smem_u32(qregion);
+  const uint32_t qlo_s = qhi_s + ROWS * 512;
+  const int n_lo_k = p.q_lo_dims / 16;
+
+  while (pre < g1 && u < n_units) {
+    const UnitInfo ui = unit_info(p, u);
+    const int nt_unit = (ui.len + SK_TK - 1) / SK_TK;
+    const int t0 = (int)(max(g0, pre) - pre), t1 = (int)(min(g1, pre + nt_unit) - pre);
+    const int R = ui.ntok * GROUP;
+    const bool whole = (t0 == 0 && t1 == nt_unit);
+
+    // ---- stage Q: rotate, split into bf16 hi (+ lo), zero the padding rows ----
+    consumer_sync(NCT);  // the previous segment is done with this region
+    for (int idx = tid; idx < ROWS * 32; idx += NCT) {
+      const int row = idx >> 5, c16 = idx & 31;  // 8 channels d = c16*8 .. +7
+      if (p.do_rope && c16 < 8) continue;        // rotary channels are written pair-wise below
+      const int b = row / GROUP, hh = row % GROUP;
+      const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
+      float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (row < R) load8<TIn>(reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM + c16 * 8, x);
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        hi[j] = pack_bf16(x[2 * j], x[2 * j + 1]);
+        lo[j] = pack_bf16(x[2 * j] - bf16lo(hi[j]), x[2 * j + 1] - bf16hi(hi[j]));
+      }
+      *reinterpret_cast<uint4 *>(qregion + q_hi_off(row, c16 * 8)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      if (c16 * 8 < p.q_lo_dims)
+        *reinterpret_cast<uint4 *>(qregion + ROWS * 512 + q_hi_off(row, c16 * 8)) =
+            make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+    if (p.do_rope) {
+      for (int idx = tid; idx < ROWS * ROT_PAIRS; idx += NCT) {
+        const int row = idx / ROT_PAIRS, i = idx % ROT_PAIRS;  // pair (i, i + 32) of this row
+        const int b = row / GROUP, hh = row % GROUP;
+        float xr = 0.f, yr = 0.f;
+        if (row < R) {
+          const size_t trow = (size_t)ui.s * p.n_new + ui.tok0 + b;
+          const size_t grow = trow * p.q_heads + (size_t)ui.kvh * GROUP + hh;
+          const TIn *src = reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM;
+          const double x = load_as_f32<TIn>(src + i), y = load_as_f32<TIn>(src + i + ROT_PAIRS);
+          const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.pos + ui.tok0 + b;
+          double c, sn;
+          rope_sincos_exact(pz, p.rope.inv_freq[i], c, sn);
+          xr = (float)(x * c - y * sn);
+          yr = (float)(x * sn + y * c);
+        }
+        const uint16_t xh = f32_to_bf16_bits(xr), yh = f32_to_bf16_bits(yr);
+        *reinterpret_cast<uint16_t *>(qregion + q_hi_off(row, i)) = xh;
+        *reinterpret_cast<uint16_t *>(qregion + q_hi_off(row, i + ROT_PAIRS)) = yh;
+        if (p.q_lo_dims) {
+          *reinterpret_cast<uint16_t *>(qregion + ROWS * 512 + q_hi_off(row, i)) =
+              f32_to_bf16_bits(xr - bf16_bits_to_f32(xh));
+          *reinterpret_cast<uint16_t *>(qregion + ROWS * 512 + q_hi_off(row, i + ROT_PAIRS)) =
+              f32_to_bf16_bits(yr - bf16_bits_to_f32(yh));
+        }
+      }
+    }
+    consumer_sync(NCT);
+
+    // ---- per-row state ----
+    float o[MT][NT_O][4];
+    float m_run[MT][2], l_run[MT][2];
+    int lim[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        m_run[mt][h2] = -INFINITY;
+        l_run[mt][h2] = 0.f;
+        const int row = mt * 16 + h2 * 8 + qd;
+        const int b = min(row / GROUP, ui.ntok - 1);
+        lim[mt][h2] = ui.pos + ui.tok0 + b + 1;  // keys visible to this row
+      }
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[mt][n][j] = 0.f;
+    }
+    const int lim_min = ui.pos + ui.tok0 + 1;
+
+    for (int t = t0; t < t1; ++t, ++it) {
+      const int st = it % STAGES;
+      if (ok && !mbar_wait(&full[st], (it / STAGES) & 1)) {
+        ok = false;
+        if (lane == 0 && p.status) *p.status = DEV_ERR_FULL_WAIT;
+      }
+      if (ok) {
+        const uint32_t kbase = smem_u32(stage_base + st * SK_STAGE_BYTES);
+        const uint32_t vbase = kbase + SK_TILE_BYTES;
+        const int key0 = t * SK_TK + ks * 16;  // first key of this warp's slice
+
+        // S = Q K^T on the 16-key slice, two accumulator sets to shorten the dependency chain
+        float s[MT][2][4], s2[MT][2][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { s[mt][n][j] = 0.f; s2[mt][n][j] = 0.f; }
+
+        const int krow = ks * 16 + (lane & 7) + ((lane >> 4) << 3);  // ldmatrix row address: key
+        const int kc_sel = (lane >> 3) & 1;                          // which 8-wide d half
+        const int arow = (lane & 7) + (((lane >> 3) & 1) << 3);      // A-fragment row within 16
+        const int ac_sel = lane >> 4;
+#pragma unroll 4
+        for (int kk = 0; kk < 16; ++kk) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(kbase + kv_tile_off<SK_TK>(krow, kk * 16 + kc_sel * 8), b0, b1, b2, b3);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4(qhi_s + q_hi_off(mt * 16 + arow, kk * 16 + ac_sel * 8), a0, a1, a2, a3);
+            if (kk & 1) {
+              mma_bf16_16816(s2[mt][0], a0, a1, a2, a3, b0, b1);
+              mma_bf16_16816(s2[mt][1], a0, a1, a2, a3, b2, b3);
+            } else {
+              mma_bf16_16816(s[mt][0], a0, a1, a2, a3, b0, b1);
+              mma_bf16_16816(s[mt][1], a0, a1, a2, a3, b2, b3);
+            }
+          }
+        }
+        for (int kk = 0; kk < n_lo_k; ++kk) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(kbase + kv_tile_off<SK_TK>(krow, kk * 16 + kc_sel * 8), b0, b1, b2, b3);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4(qlo_s + q_hi_off(mt * 16 + arow, kk * 16 + ac_sel * 8), a0, a1, a2, a3);
+            mma_bf16_16816(s2[mt][0], a0, a1, a2, a3, b0, b1);
+            mma_bf16_16816(s2[mt][1], a0, a1, a2, a3, b2, b3);
+          }
+        }
+
+        const bool need_mask = (t * SK_TK + SK_TK > lim_min);
+        // A partially valid last tile: rows of V past the unit's length may hold anything
+        // (even NaN patterns), and 0 * NaN would poison the accumulators -- zero them.
+        if (t == nt_unit - 1 && key0 + 16 > ui.len) {
+          const int valid = max(0, ui.len - key0);
+          for (int idx = lane; idx < 16 * (DW / 8); idx += 32) {
+            const int kr = idx / (DW / 8), c = idx % (DW / 8);
+            if (kr >= valid)
+              *reinterpret_cast<uint4 *>(stage_base + st * SK_STAGE_BYTES + SK_TILE_BYTES +
+                                         kv_tile_off<SK_TK>(ks * 16 + kr, ds * DW + c * 8)) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async();
+          __syncwarp();
+        }
+
+        uint32_t phi[MT][4], plo[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            float v[4];
+            v[0] = s[mt][0][2 * h2] + s2[mt][0][2 * h2];
+            v[1] = s[mt][0][2 * h2 + 1] + s2[mt][0][2 * h2 + 1];
+            v[2] = s[mt][1][2 * h2] + s2[mt][1][2 * h2];
+            v[3] = s[mt][1][2 * h2 + 1] + s2[mt][1][2 * h2 + 1];
+            if (need_mask) {
+              const int kcol = key0 + ql * 2;
+              if (kcol >= lim[mt][h2]) v[0] = -INFINITY;
+              if (kcol + 1 >= lim[mt][h2]) v[1] = -INFINITY;
+              if (kcol + 8 >= lim[mt][h2]) v[2] = -INFINITY;
+              if (kcol + 9 >= lim[mt][h2]) v[3] = -INFINITY;
+            }
+            float mxv = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+            mxv = fmaxf(mxv, __shfl_xor_sync(0xffffffffu, mxv, 1));
+            mxv = fmaxf(mxv, __shfl_xor_sync(0xffffffffu, mxv, 2));
+            const float m_new = fmaxf(m_run[mt][h2], mxv * p.scale_log2);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = fast_exp2(m_run[mt][h2] - m_use);
+            m_run[mt][h2] = m_new;
+            float pv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pv[j] = fast_exp2(fmaf(v[j], p.scale_log2, -m_use));
+            l_run[mt][h2] = l_run[mt][h2] * alpha + ((pv[0] + pv[1]) + (pv[2] + pv[3]));
+            if (alpha != 1.f) {
+#pragma unroll
+              for (int n = 0; n < NT_O; ++n) { o[mt][n][2 * h2] *= alpha; o[mt][n][2 * h2 + 1] *= alpha; }
+            }
+            // A fragment of P: a0/a2 = rows qd (h2 = 0), a1/a3 = rows qd + 8 (h2 = 1)
+            const uint32_t h01 = pack_bf16(pv[0], pv[1]), h23 = pack_bf16(pv[2], pv[3]);
+            phi[mt][h2] = h01;
+            phi[mt][2 + h2] = h23;
+            plo[mt][h2] = pack_bf16(pv[0] - bf16lo(h01), pv[1] - bf16hi(h01));
+            plo[mt][2 + h2] = pack_bf16(pv[2] - bf16lo(h23), pv[3] - bf16hi(h23));
+          }
+        }
+
+        // O += P V on this warp's 16 keys and DW output channels
+        const int vrow = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        const int vc_sel = lane >> 4;
+#pragma unroll
+        for (int n2 = 0; n2 < NT_O / 2; ++n2) {
+          uint32_t v0, v1, v2, v3;
+          ldsm_x4_trans(vbase + kv_tile_off<SK_TK>(vrow, ds * DW + n2 * 16 + vc_sel * 8), v0, v1, v2, v3);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_bf16_16816(o[mt][2 * n2], phi[mt][0], phi[mt][1], phi[mt][2], phi[mt][3], v0, v1);
+            mma_bf16_16816(o[mt][2 * n2 + 1], phi[mt][0], phi[mt][1], phi[mt][2], phi[mt][3], v2, v3);
+            mma_bf16_16816(o[mt][2 * n2], plo[mt][0], plo[mt][1], plo[mt][2], plo[mt][3], v0, v1);
+            mma_bf16_16816(o[mt][2 * n2 + 1], plo[mt][0], plo[mt][1], plo[mt][2], plo[mt][3], v2, v3);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[st]);
+    }
+
+    // ---- merge the SK_KS key-slice warps of each channel group, in slice order ----
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        float l = l_run[mt][h2];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        l_run[mt][h2] = l;
+        if (ds == 0 && ql == 0) {
+          mx[ks * ROWS + mt * 16 + h2 * 8 + qd] = m_run[mt][h2];
+          lx[ks * ROWS + mt * 16 + h2 * 8 + qd] = l;
+        }
+      }
+    consumer_sync(NCT);  // also: every warp is past its last tile, the Q area may be reused
+    float *comb = reinterpret_cast<float *>(qregion);  // [ROWS][256] fp32, 8-float groups XOR (row & 7)
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int row = mt * 16 + h2 * 8 + qd;
+        float mg = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < SK_KS; ++k) mg = fmaxf(mg, mx[k * ROWS + row]);
+        const float m_use = (mg == -INFINITY) ? 0.f : mg;
+        const float f = fast_exp2(m_run[mt][h2] - m_use);
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) { o[mt][n][2 * h2] *= f; o[mt][n][2 * h2 + 1] *= f; }
+      }
+    for (int k = 0; k < SK_KS; ++k) {
+      if (ks == k) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const int row = mt * 16 + h2 * 8 + qd;
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n) {
+              const int d = ds * DW + n * 8 + ql * 2;
+              float2 *dst = reinterpret_cast<float2 *>(comb + row * HEAD_DIM + (d ^ ((row & 7) << 3)));
+              float2 v = make_float2(o[mt][n][2 * h2], o[mt][n][2 * h2 + 1]);
+              if (k) { const float2 w = *dst; v.x += w.x; v.y += w.y; }
+              *dst = v;
+            }
+          }
+      }
+      consumer_sync(NCT);
+    }
+
+    // ---- finish the segment: final output, or a partial for the merge kernel ----
+    for (int idx = tid; idx < R * 32; idx += NCT) {
+      const int row = idx >> 5, c8 = idx & 31;  // channels c8*8 .. +7
+      float mg = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < SK_KS; ++k) mg = fmaxf(mg, mx[k * ROWS + row]);
+      const float m_use = (mg == -INFINITY) ? 0.f : mg;
+      float lg = 0.f;
+#pragma unroll
+      for (int k = 0; k < SK_KS; ++k) lg += lx[k * ROWS + row] * fast_exp2(mx[k * ROWS + row] - m_use);
+      const float4 *srcp = reinterpret_cast<const float4 *>(comb + row * HEAD_DIM + ((c8 * 8) ^ ((row & 7) << 3)));
+      const float4 a = srcp[0], bq = srcp[1];
+      float v[8] = {a.x, a.y, a.z, a.w, bq.x, bq.y, bq.z, bq.w};
+      const int b = row / GROUP, hh = row % GROUP;
+      const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
+      if (whole && !p.partial_out) {
+        const float inv = 1.f / lg;
+        if (p.do_gate) {
+          const uint4 g4 = *reinterpret_cast<const uint4 *>(p.gate + grow * HEAD_DIM + c8 * 8);
+          const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[2 * j] *= inv * sigmoidf_(bf16lo(gw[j]));
+            v[2 * j + 1] *= inv * sigmoidf_(bf16hi(gw[j]));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] *= inv;
+        }
+        store8<TOut>(reinterpret_cast<TOut *>(p.out) + grow * HEAD_DIM + c8 * 8, v);
+        if (c8 == 0 && p.lse) p.lse[grow] = (mg + log2f(lg)) * LN2;
+      } else {
+        float *dst = (whole && p.partial_out)
+                         ? p.partial_out + grow * PART_STRIDE
+                         : p.ws + ((size_t)(cta + u) * (p.rb * GROUP) + row) * PART_STRIDE;
+        *reinterpret_cast<float4 *>(dst + c8 * 8) = a;
+        *reinterpret_cast<float4 *>(dst + c8 * 8 + 4) = bq;
+        if (c8 == 0) { dst[256] = mg; dst[257] = lg; }
+      }
+    }
+    pre += nt_unit;
+    ++u;
+  }
+}
+
+// Merge the partials of every unit that was cut across CTAs.  One block per unit, one warp per
+// row, lane = 8 channels; partials are visited in CTA order so the sum order is fixed.
+template <typename TOut>
+__global__ void __launch_bounds__(256) splitkv_merge_kernel(const __grid_constant__ SplitKVParams p) {
+  const int u = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_units = p.n_seq * p.nblk * p.kv_heads;
+  __shared__ long long sh[2];
+  if (warp == 0) {
+    const long long total = warp_total_tiles(p, n_units, lane);
+    const long long pre = warp_unit_prefix(p, u, lane);
+    if (lane == 0) { sh[0] = total; sh[1] = pre; }
+  }
+  __syncthreads();
+  const long long total = sh[0], pre = sh[1];
+  const UnitInfo ui = unit_info(p, u);
+  const int nt = (ui.len + SK_TK - 1) / SK_TK;
+  if (nt == 0 || total == 0) return;
+  const int c_first = cta_of_tile(pre, total, p.G), c_last = cta_of_tile(pre + nt - 1, total, p.G);
+  if (c_first == c_last) return;  // the main kernel already wrote this unit
+  const int R = ui.ntok * GROUP;
+  for (int row = warp; row < R; row += 8) {
+    float mg = -INFINITY;
+    for (int c = c_first; c <= c_last; ++c) {
+      const float *src = p.ws + ((size_t)(c + u) * (p.rb * GROUP) + row) * PART_STRIDE;
+      if (src[257] > 0.f) mg = fmaxf(mg, src[256]);
+    }
+    const float m_use = (mg == -INFINITY) ? 0.f : mg;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float lg = 0.f;
+    for (int c = c_first; c <= c_last; ++c) {
+      const float *src = p.ws + ((size_t)(c + u) * (p.rb * GROUP) + row) * PART_STRIDE;
+      const float l = src[257];
+      if (!(l > 0.f)) continue;
+      const float f = fast_exp2(src[256] - m_use);
+      lg += l * f;
+      const float4 a = *reinterpret_cast<const float4 *>(src + lane * 8);
+      const float4 b = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
+      acc[0] += a.x * f; acc[1] += a.y * f; acc[2] += a.z * f; acc[3] += a.w * f;
+      acc[4] += b.x * f; acc[5] += b.y * f; acc[6] += b.z * f; acc[7] += b.w * f;
+    }
+    const int b = row / GROUP, hh = row % GROUP;
+    const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
+    if (p.partial_out) {
+      float *dst = p.partial_out + grow * PART_STRIDE;
+      *reinterpret_cast<float4 *>(dst + lane * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4 *>(dst + lane * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      if (lane == 0) { dst[256] = mg; dst[257] = lg; }
+      continue;
+    }
+    const float inv = 1.f / lg;
+    if (p.do_gate) {
+      const uint4 g4 = *reinterpret_cast<const uint4 *>(p.gate + grow * HEAD_DIM + lane * 8);
+      const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] *= inv * sigmoidf_(bf16lo(gw[j]));
+        acc[2 * j + 1] *= inv * sigmoidf_(bf16hi(gw[j]));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] *= inv;
+    }
+    store8<TOut>(reinterpret_cast<TOut *>(p.out) + grow * HEAD_DIM + lane * 8, acc);
+    if (lane == 0 && p.lse) p.lse[grow] = (mg + log2f(lg)) * LN2;
+  }
+}
+
+// Merge n_parts partial sets [n_parts][n][PART_STRIDE] (n = rows * q_heads) in index order, then
+// normalise and gate.  One warp per (row, head), lane = 8 channels.
+template <typename TOut>
+__global__ void __launch_bounds__(256) combine_partials_kernel(const float *parts, int n_parts, long long n,
+                                                               const uint16_t *gate, TOut *out, float *lse) {
+  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= n) return;
+  float mg = -INFINITY;
+  for (int k = 0; k < n_parts; ++k) {
+    const float *src = parts + ((size_t)k * n + r) * PART_STRIDE;
+    if (src[257] > 0.f) mg = fmaxf(mg, src[256]);
+  }
+  const float m_use = (mg == -INFINITY) ? 0.f : mg;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float lg = 0.f;
+  for (int k = 0; k < n_parts; ++k) {
+    const float *src = parts + ((size_t)k * n + r) * PART_STRIDE;
+    const float l = src[257];
+    if (!(l > 0.f)) continue;
+    const float f = fast_exp2(src[256] - m_use);
+    lg += l * f;
+    const float4 a = *reinterpret_cast<const float4 *>(src + lane * 8);
+    const float4 b = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
+    acc[0] += a.x * f; acc[1] += a.y * f; acc[2] += a.z * f; acc[3] += a.w * f;
+    acc[4] += b.x * f; acc[5] += b.y * f; acc[6] += b.z * f; acc[7] += b.w * f;
+  }
+  const float inv = 1.f / lg;
+  if (gate) {
+    float g[8];
+    load8<uint16_t>(gate + r * HEAD_DIM + lane * 8, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv * sigmoidf_(g[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv;
+  }
+  store8<TOut>(out + r * HEAD_DIM + lane * 8, acc);
+  if (lane == 0 && lse) lse[r] = (mg + log2f(lg)) * LN2;
+}
+
+template <int MT, int DS, int STAGES>
+constexpr size_t splitkv_smem_bytes() {
+  return 1024 + (size_t)STAGES * SK_STAGE_BYTES + (size_t)MT * 16 * 1024 + 2 * SK_KS * MT * 16 * 4 +
+         2 * STAGES * 8 + 3 * 8 + 64;
+}
+
+}  // namespace qwb

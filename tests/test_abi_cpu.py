@@ -1,0 +1,50 @@
+"""CPU tests of the C-ABI library: it builds, loads, and exports every declared symbol.
+No compute entry point is called here (no GPU)."""
+import ctypes
+import os
+import re
+
+from qwengine_b200 import api, build
+from tests.conftest import ROOT
+
+
+def _declared():
+    names = set()
+    for fn in os.listdir(os.path.join(ROOT, "include")):
+        text = open(os.path.join(ROOT, "include", fn)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(qw_[a-z0-9_]+)\s*\(", text))
+    return names
+
+
+def test_library_builds_and_exports_every_declared_symbol():
+    path = build.build()
+    assert os.path.exists(path)
+    l = ctypes.CDLL(path)
+    declared = _declared()
+    assert len(declared) >= 20
+    missing = [n for n in sorted(declared) if not hasattr(l, n)]
+    assert not missing, "declared in include/ but not exported: %s" % missing
+    # the binding covers the same set
+    assert declared == set(api._SIGS), (declared ^ set(api._SIGS))
+
+
+def test_host_only_entry_points():
+    l = api.lib()
+    assert l.qw_abi_version() == 1
+    assert l.qw_strerror(0) == b"ok" and b"geometry" in l.qw_strerror(2)
+    assert l.qw_attn_decode_scratch_floats(24, 4, 8192, 1) <= 1 * 24 * 8192
+    assert l.qw_attn_decode_scratch_floats(24, 4, 512, 8) <= 8 * 24 * 512
+
+
+def test_argument_validation_needs_no_gpu():
+    l = api.lib()
+    assert l.qw_rope_bf16(None, 24, 256, 64, None, 1e7, None, 1, None) == 1       # null pointers
+    assert l.qw_gate_sigmoid_f32(None, None, 8, None) == 1
+    d = api.MixerDesc()
+    assert l.qw_mixer_forward(ctypes.byref(d), None) == 1
+    buf = (ctypes.c_float * 16)()
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert l.qw_rope_f32(p, 24, 128, 64, p, 1e7, None, 1, None) == 2               # head_dim 128 unsupported
+    assert l.qw_attn_decode_f32(p, p, p, p, p, 256, 3, 18, 0.0625, p, 64, 1, None) == 2   # 3 kv heads
+    assert l.qw_attn_decode_f32(p, p, p, p, p, 256, 4, 24, 0.0625, p, 64, 9, None) == 2   # B > 8
