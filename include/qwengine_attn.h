@@ -161,6 +161,14 @@ int qw_mixer_forward(const qw_mixer_desc *d, qw_stream stream);
 /* Number of kernels the last qw_* call on this thread launched (for launch accounting). */
 int qw_last_launch_count(void);
 
+/* Instrumentation for benchmarks.  While enabled (per host thread), every attention call
+ * records a CUDA event pair around its dominant kernel (split-KV or tcgen05 prefill) on the
+ * launching stream.  qw_profile_last_kernel_ms() waits for that kernel and returns its
+ * duration; not for use inside a stream capture.  Enabling creates the two events once.
+ * No counterpart in the reference, which times whole graphs (bench/spec_budget.cu:38-54). */
+int qw_profile_enable(int on);
+int qw_profile_last_kernel_ms(float *ms);
+
 /* ------------------------------------------------------------------------------------------
  * Cross-GPU split-KV combine (used only where one sequence's KV range is split across GPUs)
  *

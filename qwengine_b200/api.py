@@ -40,6 +40,8 @@ _SIGS = {
     "qw_abi_version": (_i, []),
     "qw_last_cuda_error": (C.c_char_p, []),
     "qw_last_launch_count": (_i, []),
+    "qw_profile_enable": (_i, [_i]),
+    "qw_profile_last_kernel_ms": (_i, [C.POINTER(C.c_float)]),
     "qw_rope_bf16": (_i, [_vp, _i, _i, _i, _vp, _f, _vp, _i, _vp]),
     "qw_rope_f32": (_i, [_vp, _i, _i, _i, _vp, _f, _vp, _i, _vp]),
     "qw_kv_append_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
@@ -181,6 +183,16 @@ class Mixer:
         code = int(self.status.item())
         if code:
             raise QwError("kernel reported device error code %d" % code)
+
+
+def profile_enable(on=True):
+    _check(lib().qw_profile_enable(1 if on else 0))
+
+
+def profile_last_kernel_ms():
+    ms = C.c_float()
+    _check(lib().qw_profile_last_kernel_ms(C.byref(ms)))
+    return ms.value
 
 
 def _addr(t):

@@ -35,6 +35,17 @@ int check_launch(const char *what) {
   return e == cudaSuccess ? QW_OK : cuda_fail(e, what);
 }
 
+// Optional event pair around the dominant kernel of a call (see qw_profile_enable).
+thread_local bool g_prof_on = false;
+thread_local cudaEvent_t g_prof_ev[2] = {nullptr, nullptr};
+thread_local bool g_prof_valid = false;
+void prof_mark(int which, cudaStream_t st) {
+  if (g_prof_on && g_prof_ev[which]) {
+    cudaEventRecord(g_prof_ev[which], st);
+    if (which == 1) g_prof_valid = true;
+  }
+}
+
 bool geometry_ok(int dim, int kv_heads, int q_heads) {
   return dim == HEAD_DIM && (kv_heads == 1 || kv_heads == 2 || kv_heads == 4) && q_heads == GROUP * kv_heads;
 }
@@ -133,7 +144,9 @@ int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKV
     QW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured[dev] = true;
   }
+  prof_mark(0, st);
   kern<<<p.G, (SK_KS * DS + 1) * 32, smem, st>>>(mk, mv, p);
+  prof_mark(1, st);
   int rc = check_launch("splitkv_kernel");
   if (rc) return rc;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
@@ -220,7 +233,9 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
     pc.do_rope = (d->flags & QW_F_ROPE) != 0; pc.status = d->status;
     pc.rope = tab;
     int n = 0;
+    prof_mark(0, st);
     int rc = launch_prefill_umma(pc, st, &n);
+    prof_mark(1, st);
     g_launches += n;
     if (rc == QW_ERR_CUDA) {
       cudaError_t e = cudaGetLastError();
@@ -279,6 +294,22 @@ const char *qw_strerror(int code) {
 int qw_abi_version(void) { return 1; }
 const char *qw_last_cuda_error(void) { return g_cuda_err; }
 int qw_last_launch_count(void) { return g_launches; }
+
+int qw_profile_enable(int on) {
+  if (on && !g_prof_ev[0]) {
+    QW_CUDA(cudaEventCreate(&g_prof_ev[0]));
+    QW_CUDA(cudaEventCreate(&g_prof_ev[1]));
+  }
+  g_prof_on = on != 0;
+  g_prof_valid = false;
+  return QW_OK;
+}
+int qw_profile_last_kernel_ms(float *ms) {
+  if (!ms || !g_prof_valid) return QW_ERR_ARG;
+  QW_CUDA(cudaEventSynchronize(g_prof_ev[1]));
+  QW_CUDA(cudaEventElapsedTime(ms, g_prof_ev[0], g_prof_ev[1]));
+  return QW_OK;
+}
 
 int qw_rope_bf16(qw_bf16 *v, int heads, int dim, int rot, const int *dpos, float theta, qw_stream stream, int B,
                  const int *mpos) {

@@ -1,0 +1,235 @@
+"""Parity of the CUDA path against the CPU oracle, through the C ABI.  Needs a B200."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import pyoracle as O
+from qwengine_b200 import api
+from tests.gpu_util import dev_bf16, dev_bits, host_bits, host_f32, run_case
+from tests.util import Case, bf16_exact, check_lse, check_out, check_out_bf16, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def _full_check(c, what):
+    ref, lse_ref, kc_ref, vc_ref = c.oracle()
+    o32, lse, kc, vc, _ = run_case(c, out_f32=True)
+    assert np.array_equal(kc, kc_ref), what + ": appended K rows differ from the oracle (bit-exact expected)"
+    assert np.array_equal(vc, vc_ref), what + ": appended V rows differ"
+    check_out(o32, ref, what + " fp32 out")
+    check_lse(lse, lse_ref, what)
+    o16, lse16, _, _, _ = run_case(c, out_f32=False)
+    check_out_bf16(o16, ref, what + " bf16 out")
+    # the bf16 output is the rounding of the fp32 output
+    assert np.array_equal(O.f32_to_bf16_bits(o32), O.f32_to_bf16_bits(o16))
+    assert np.array_equal(lse, lse16)
+
+
+# ---- small kernels ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("pos0,B,use_mpos", [(0, 1, False), (8192, 4, False), (131071, 3, False), (17, 5, True)])
+def test_rope(dtype, pos0, B, use_mpos):
+    rng = np.random.default_rng(1)
+    v = bf16_exact(rng, (B, 24, 256))
+    mpos = None
+    if use_mpos:
+        t = pos0 + np.arange(B)
+        mpos = np.stack([t, t + 2, 3 * t], -1).astype(np.int32)
+    ref = O.rope_f32(v.copy(), pos0, mpos=mpos)
+    t = torch.from_numpy(v).cuda().to(dtype)
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    api.rope(t, 24, 256, 64, dpos, 1e7, B=B, mpos=None if mpos is None else torch.from_numpy(mpos).cuda())
+    got = host_f32(t)
+    if dtype == torch.float32:
+        assert np.abs(got - ref).max() <= 2e-7 * max(1.0, np.abs(ref).max())
+    else:
+        assert np.array_equal(O.f32_to_bf16_bits(got), O.f32_to_bf16_bits(ref))
+    assert np.array_equal(got[..., 64:], v[..., 64:])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_kv_append(dtype):
+    rng = np.random.default_rng(2)
+    B, ctx, pos0 = 5, 64, 37
+    k, v = bf16_exact(rng, (B, 1024)), bf16_exact(rng, (B, 1024))
+    kc = torch.zeros(ctx, 1024, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    api.kv_append(torch.from_numpy(k).cuda().to(dtype), torch.from_numpy(v).cuda().to(dtype), kc, vc, dpos, 1024, B=B)
+    want_k = np.zeros((ctx, 1024), np.float32)
+    want_k[pos0:pos0 + B] = k
+    want_v = np.zeros((ctx, 1024), np.float32)
+    want_v[pos0:pos0 + B] = v
+    assert np.array_equal(host_f32(kc), want_k) and np.array_equal(host_f32(vc), want_v)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gate_sigmoid(dtype):
+    rng = np.random.default_rng(3)
+    x, g = bf16_exact(rng, (3 * 6144,)), bf16_exact(rng, (3 * 6144,))
+    ref = O.gate_sigmoid_f32(x.copy(), g)
+    t = torch.from_numpy(x).cuda().to(dtype)
+    api.gate_sigmoid(t, torch.from_numpy(g).cuda().to(dtype), x.size)
+    got = host_f32(t)
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert np.abs(got - ref).max() <= tol * max(1.0, np.abs(ref).max())
+
+
+# ---- fused mixer: decode and verify --------------------------------------------------------------------
+@pytest.mark.parametrize("hist", [[0], [1], [62], [63], [64], [65], [127, 128, 129], [1000, 3, 517, 64]])
+def test_decode_small(hist):
+    _full_check(Case(10 + len(hist), hist, 1), "decode hist=%s" % hist)
+
+
+@pytest.mark.parametrize("n_new", [2, 3, 4, 5, 6, 8])
+def test_verify_rows(n_new):
+    _full_check(Case(20 + n_new, [300, 61, 0, 1999], n_new), "verify B=%d" % n_new)
+
+
+@pytest.mark.parametrize("kv_heads", [1, 2])
+def test_kv_head_shards(kv_heads):
+    _full_check(Case(31, [700, 129], 4, kv_heads=kv_heads), "kv_heads=%d" % kv_heads)
+
+
+def test_mrope_positions():
+    _full_check(Case(32, [40, 7], 3, mrope=True), "mrope")
+
+
+def test_no_gate_no_lse_and_flags():
+    c = Case(33, [200], 2, gate=False)
+    ref, _, _, _ = c.oracle(do_gate=False)
+    o32, lse, _, _, _ = run_case(c, out_f32=True, lse=False)
+    check_out(o32, ref, "no gate")
+
+
+def test_config2_shape_reduced():
+    """BASELINE config 2 at a history the oracle finishes quickly: 16 sequences, 1 query each."""
+    _full_check(Case(40, [2048] * 16, 1), "config2-reduced")
+
+
+def test_config3_shape_reduced():
+    """BASELINE config 3 shape: 8 sequences x 4 draft tokens, ragged histories."""
+    rng = np.random.default_rng(41)
+    _full_check(Case(41, rng.integers(256, 4096, 8).tolist(), 4), "config3-reduced")
+
+
+def test_bitwise_repeatable():
+    c = Case(42, [3000, 500, 64, 9000], 4)
+    a = run_case(c)
+    b = run_case(c)
+    d = run_case(c)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[0], d[0]) and np.array_equal(a[1], b[1])
+
+
+def test_stale_rows_beyond_position_are_never_read():
+    """Cache rows past a sequence's position hold anything (the reference never clears them,
+    src/model.cu:77-79,195-202); NaN patterns there must not leak into the result."""
+    c = Case(43, [100, 64], 2, pad_rows=130)
+    c.kc0[c.kc0 == 0x4F00] = 0x7FC0  # NaN
+    c.vc0[c.vc0 == 0x4F00] = 0x7FC0
+    ref, lse_ref, _, _ = c.oracle()
+    o32, lse, _, _, _ = run_case(c, out_f32=True)
+    assert np.isfinite(o32).all()
+    check_out(o32, ref, "stale rows")
+    check_lse(lse, lse_ref, "stale rows")
+
+
+# ---- prefill through the split-KV kernel (short chunks and the forced fallback) ------------------------
+@pytest.mark.parametrize("hist,T", [(0, 16), (0, 64), (100, 40), (0, 129)])
+def test_prefill_chunk_splitkv(hist, T):
+    c = Case(50 + T, [hist], T, kv_heads=2)
+    ref, lse_ref, kc_ref, _ = c.oracle()
+    o32, lse, kc, _, _ = run_case(c, out_f32=True, flags=api.F_ROPE | api.F_APPEND | api.F_GATE | api.F_NO_UMMA)
+    assert np.array_equal(kc, kc_ref)
+    check_out(o32, ref, "prefill splitkv")
+    check_lse(lse, lse_ref, "prefill splitkv")
+
+
+# ---- drop-in launchers with the reference's argument lists ------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B", [1, 4, 8])
+def test_dropin_sequence_like_model_cu(dtype, B):
+    """rope(q), rope(k), k_kv_append, k_attn_decode, k_gate_sigmoid in the order of
+    src/model.cu:228-240, one sequence, device-resident position."""
+    ctx, pos0 = 2048, 777
+    c = Case(60 + B, [pos0], B, pad_rows=ctx - pos0 - B)
+    ref, _, kc_ref, vc_ref = c.oracle()
+    q = torch.from_numpy(c.q[0]).cuda().to(dtype)
+    k = torch.from_numpy(c.k[0]).cuda().to(dtype)
+    v = torch.from_numpy(c.v[0]).cuda().to(dtype)
+    gate = torch.from_numpy(c.gate[0]).cuda().to(dtype)
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    scratch = torch.empty(B * 24 * ctx, dtype=torch.float32, device="cuda")  # the reference's size
+    api.rope(q, 24, 256, 64, dpos, 1e7, B=B)
+    api.rope(k, 4, 256, 64, dpos, 1e7, B=B)
+    api.kv_append(k, v, kc, vc, dpos, 1024, B=B)
+    api.attn_decode(q, kc, vc, out, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, B=B)
+    api.gate_sigmoid(out, gate, out.numel())
+    torch.cuda.synchronize()
+    got = host_f32(out)
+    assert np.array_equal(host_bits(kc), kc_ref) and np.array_equal(host_bits(vc), vc_ref)
+    if dtype == torch.float32:
+        check_out(got, ref, "drop-in f32")
+    else:
+        # q is rounded to bf16 after RoPE and the attention output before the gate: two extra
+        # roundings the fused path does not have
+        assert np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 4e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_dropin_prefill_like_prefill_cu(dtype):
+    ctx, pos0, T = 512, 100, 50
+    c = Case(70, [pos0], T, pad_rows=ctx - pos0 - T)
+    ref, _, _, _ = c.oracle(do_gate=False)
+    q = torch.from_numpy(c.q[0]).cuda().to(dtype)
+    k = torch.from_numpy(c.k[0]).cuda().to(dtype)
+    v = torch.from_numpy(c.v[0]).cuda().to(dtype)
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    scratch = torch.empty(api.attn_prefill_scratch_floats(24, 4, ctx, T), dtype=torch.float32, device="cuda")
+    api.rope(q, 24, 256, 64, dpos, 1e7, B=T)
+    api.rope(k, 4, 256, 64, dpos, 1e7, B=T)
+    api.kv_append(k, v, kc, vc, dpos, 1024, B=T)
+    api.attn_prefill(q, kc, vc, out, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, T)
+    torch.cuda.synchronize()
+    got = host_f32(out)
+    if dtype == torch.float32:
+        check_out(got, ref, "drop-in prefill f32")
+    else:
+        assert np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 4e-3
+
+
+def test_graph_capture_and_replay_advances_with_device_position():
+    """The decode launch is legal inside a stream capture and reads its position on the device,
+    like the reference's replayed decode graph (src/model.cu:318-327)."""
+    ctx = 1024
+    c = Case(80, [300], 1, pad_rows=ctx - 301)
+    q = dev_bf16(c.q[0])
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    dpos = torch.tensor([300], dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    scratch = torch.empty(24 * ctx, dtype=torch.float32, device="cuda")
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        api.attn_decode(q, kc, vc, out, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, B=1, stream=s)  # warm-up
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            api.attn_decode(q, kc, vc, out, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, B=1, stream=s)
+    outs = []
+    for p in (300, 150, 299):
+        dpos.fill_(p)
+        g.replay()
+        torch.cuda.synchronize()
+        outs.append(host_f32(out).copy())
+    for p, got in zip((300, 150, 299), outs):
+        cc = Case(80, [300], 1, pad_rows=ctx - 301)
+        kcn, vcn = cc.kc0.copy(), cc.vc0.copy()
+        ref, _ = O.mixer(cc.q, None, None, None, kcn, vcn, [p], do_rope=False, do_append=False, do_gate=False)
+        # row sees keys [0, p]: slot p must hold data, so only p < 300 is meaningful with this cache
+        if p < 300:
+            assert np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 4e-3
+    assert not np.array_equal(outs[1], outs[2])

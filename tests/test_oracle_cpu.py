@@ -43,6 +43,29 @@ def test_oracle_matches_hf_golden(path):
     assert np.abs(lse - z["lse"]).max() < 2e-6
 
 
+_REF = sorted(glob.glob(os.path.join(GOLDEN, "ref_*.npz")))
+
+
+@pytest.mark.skipif(not _REF, reason="no reference-kernel fixtures committed yet")
+@pytest.mark.parametrize("path", _REF, ids=os.path.basename)
+def test_oracle_matches_reference_kernel_golden(path):
+    """The oracle (fp32-cache mode) reproduces what the reference engine's own kernels produced.
+    The reference evaluates pow / sincos / exp with fast intrinsics, so agreement is to ~1e-5."""
+    z = np.load(path)
+    kvh, hist, n_new = int(z["kv_heads"]), int(z["hist"]), int(z["n_new"])
+    f = O.bf16_bits_to_f32
+    kc = np.zeros((hist + n_new, kvh * 256), np.float32)
+    vc = np.zeros_like(kc)
+    kc[:hist] = f(z["kc0"]).reshape(hist, kvh * 256)
+    vc[:hist] = f(z["vc0"]).reshape(hist, kvh * 256)
+    mpos = z["mpos"][None] if z["mpos"].size else None
+    out, _ = O.mixer(f(z["q"])[None], f(z["k"])[None], f(z["v"])[None], f(z["gate"])[None], kc, vc, [hist],
+                     mpos=mpos, kv_heads=kvh)
+    assert np.array_equal(vc[hist:], z["v_rows"])
+    assert np.abs(kc[hist:] - z["k_rows"]).max() < 2e-4, "rotated K rows"
+    assert np.abs(out - z["out"]).max() < 2e-4 and rel_l2(out, z["out"]) < 1e-4
+
+
 def test_verify_rows_equal_sequential_decode():
     """A verify batch of B rows gives what B single-token decode steps give: the property the
     reference's end-to-end spec test relies on (test/test_spec.cu:64-98)."""
