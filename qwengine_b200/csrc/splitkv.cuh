@@ -303,9 +303,13 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
 
     for (int t = t0; t < t1; ++t, ++it) {
       const int st = it % STAGES;
-      if (ok && !mbar_wait(&full[st], (it / STAGES) & 1)) {
-        ok = false;
-        if (lane == 0 && p.status) *p.status = DEV_ERR_FULL_WAIT;
+      if (ok) {
+        // every lane polls; the verdict is made warp-uniform before any warp-wide operation
+        const bool got = mbar_wait(&full[st], (it / STAGES) & 1);
+        if (!__all_sync(0xffffffffu, got)) {
+          ok = false;
+          if (lane == 0 && p.status) *p.status = DEV_ERR_FULL_WAIT;
+        }
       }
       if (ok) {
         const uint32_t kbase = smem_u32(stage_base + st * SK_STAGE_BYTES);
@@ -547,6 +551,7 @@ __global__ void __launch_bounds__(256) splitkv_merge_kernel(const __grid_constan
   for (int row = warp; row < R; row += 8) {
     float mg = -INFINITY;
     for (int c = c_first; c <= c_last; ++c) {
+      if (total * c / p.G == total * (c + 1) / p.G) continue;  // this CTA owned no tile and wrote nothing
       const float *src = p.ws + ((size_t)(c + u) * (p.rb * GROUP) + row) * PART_STRIDE;
       if (src[257] > 0.f) mg = fmaxf(mg, src[256]);
     }
@@ -554,6 +559,7 @@ __global__ void __launch_bounds__(256) splitkv_merge_kernel(const __grid_constan
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float lg = 0.f;
     for (int c = c_first; c <= c_last; ++c) {
+      if (total * c / p.G == total * (c + 1) / p.G) continue;
       const float *src = p.ws + ((size_t)(c + u) * (p.rb * GROUP) + row) * PART_STRIDE;
       const float l = src[257];
       if (!(l > 0.f)) continue;
