@@ -1,10 +1,13 @@
 """Benchmark of the full-attention mixer hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode|verify|prefill8k] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode|verify|prefill8k|prefill32k]
+                    [--impl reference]
 
-Prints ONE JSON line.  The default workload is BASELINE.json's decode configuration (16
-sequences, one query token each, 8192 cached tokens, 24/4 heads, head_dim 256, bf16).  A step
-is one fused mixer call over the whole batch: rope(q,k), KV append, attention, sigmoid gate.
+Prints ONE JSON line.  The headline workload is BASELINE.json's decode configuration (16
+sequences x 1 query token against 8192 cached tokens, 24/4 heads, head_dim 256, bf16); the same
+line carries, under "prefill", the other half of the metric: causal prefill attention at 8K
+context on the tcgen05 kernel.  A step is one fused mixer call over the whole batch: rope(q, k),
+KV append, attention, sigmoid gate.
 """
 import argparse
 import json
@@ -22,7 +25,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 KV_BYTES_PER_TOKEN = 4096  # K + V, 4 heads x 256 x bf16, for the full (unsharded) layer
-FLOPS_PER_PAIR = 24576     # 4 * head_dim * q_heads per (query, key) pair
+FLOPS_PER_PAIR = 24576     # 4 * head_dim * q_heads per unmasked (query, key) pair
 
 
 def measured_peaks():
@@ -34,7 +37,7 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -64,53 +67,61 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for l in self.lines:
             f = [x.strip() for x in l.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                sm.append(float(f[1])); mx.append(float(f[2])); pw.append(float(f[3]))
             except ValueError:
                 continue
             for n, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        # the median over samples taken under load (power above the idle floor)
+        busy = [c for c, w in zip(sm, pw) if w > 250.0] or sm
+        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(pw) if pw else None}
 
 
 def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
-def shard_plan(n_gpus, rank):
+def shard_plan(n_gpus):
     """KV-head sharding at 2 and 4 GPUs; at 8, one KV head per GPU pair and the pair splits the
-    sequences.  Returns (kv_heads_local, seq_share) where seq_share = fraction of the global
-    batch's sequences this rank serves."""
-    if n_gpus == 1:
-        return 4, 1.0
-    if n_gpus == 2:
-        return 2, 1.0
-    if n_gpus == 4:
-        return 1, 1.0
-    if n_gpus == 8:
-        return 1, 0.5
-    raise SystemExit("--gpus must be 1, 2, 4 or 8")
+    sequences.  Returns (kv_heads_local, sequence share)."""
+    plan = {1: (4, 1.0), 2: (2, 1.0), 4: (1, 1.0), 8: (1, 0.5)}
+    if n_gpus not in plan:
+        raise SystemExit("--gpus must be 1, 2, 4 or 8")
+    return plan[n_gpus]
 
 
-def build_decode_workload(name, n_gpus, rank, seed):
-    """Weak scaling: the global batch grows with N so that every GPU streams the same KV bytes
-    as the single-GPU configuration."""
-    kvh, share = shard_plan(n_gpus, rank)
-    g = torch.Generator(device="cuda").manual_seed(seed + 1000 * rank)
+WORKLOADS = {
+    # name: (sequences per GPU-equivalent, new tokens, description of the history)
+    "decode": (16, 1, "8192"),
+    "verify": (8, 4, "U[2048,32768]"),
+    "prefill8k": (1, 8192, "0 (single shot, 8K context)"),
+    "prefill32k": (1, 2048, "30720 (last 2048-token chunk of a 32K prefill)"),
+}
+
+
+def build_workload(name, n_gpus, rank, seed):
+    """Weak scaling: the global batch grows with N so that every GPU does the work of the
+    single-GPU configuration; ranks own disjoint KV heads (and, at 8, disjoint sequences)."""
+    kvh, share = shard_plan(n_gpus)
+    per, n_new, _ = WORKLOADS[name]
+    n_seq_global = per * n_gpus
     if name == "decode":
-        n_seq_global, n_new = 16 * n_gpus, 1
         hist_global = np.full(n_seq_global, 8192, np.int32)
-    else:  # verify: BASELINE config 3
-        n_seq_global, n_new = 8 * n_gpus, 4
+    elif name == "verify":
         hist_global = np.random.default_rng(seed).integers(2048, 32769 - n_new, n_seq_global).astype(np.int32)
+    elif name == "prefill8k":
+        hist_global = np.zeros(n_seq_global, np.int32)
+    else:
+        hist_global = np.full(n_seq_global, 30720, np.int32)
     n_local = int(round(n_seq_global * share))
     first = (rank // 4) * n_local if n_gpus == 8 else 0
     hist = hist_global[first:first + n_local]
@@ -119,22 +130,173 @@ def build_decode_workload(name, n_gpus, rank, seed):
     rows = int(cap.sum())
     kvdim = kvh * 256
     dev = "cuda"
-    w = {
-        "n_seq": n_local, "n_new": n_new, "kv_heads": kvh, "hist": hist,
-        "kc": torch.randn(rows, kvdim, device=dev, dtype=torch.bfloat16, generator=g),
-        "vc": torch.randn(rows, kvdim, device=dev, dtype=torch.bfloat16, generator=g),
-        "pos": torch.from_numpy(hist).to(dev), "cache_row": torch.from_numpy(cache_row).to(dev),
-    }
+    g = torch.Generator(device=dev).manual_seed(seed + 1000 * rank)
+    w = {"name": name, "n_seq": n_local, "n_seq_global": n_seq_global, "n_new": n_new, "kv_heads": kvh, "hist": hist,
+         "kc": torch.randn(rows, kvdim, device=dev, dtype=torch.bfloat16, generator=g),
+         "vc": torch.randn(rows, kvdim, device=dev, dtype=torch.bfloat16, generator=g),
+         "pos": torch.from_numpy(hist).to(dev), "cache_row": torch.from_numpy(cache_row).to(dev)}
     for k_, heads in (("q", 6 * kvh), ("gate", 6 * kvh), ("k_new", kvh), ("v_new", kvh)):
         w[k_] = torch.randn(n_local, n_new, heads, 256, device=dev, dtype=torch.bfloat16, generator=g)
     w["out"] = torch.empty_like(w["q"])
     w["lse"] = torch.empty(n_local, n_new, 6 * kvh, device=dev, dtype=torch.float32)
-    # algorithmic KV bytes of this rank: every row b reads pos + b + 1 tokens, but the n_new rows of
-    # a sequence share one pass over the cache, so bytes = (hist + n_new) tokens * K+V * local heads
+    # Algorithmic work of this rank.  KV bytes: the n_new rows of a sequence share one pass over
+    # its cache, (hist + n_new) tokens x 4096 B x (local heads / 4).  FLOPs: 24576 per unmasked pair.
     w["kv_bytes"] = float((hist.astype(np.int64) + n_new).sum()) * KV_BYTES_PER_TOKEN * kvh / 4
     pairs = sum(int(h) * n_new + n_new * (n_new + 1) // 2 for h in hist)
     w["flops"] = float(pairs) * FLOPS_PER_PAIR * kvh / 4
     return w
+
+
+def measure(name, args, rank, world, flags_extra=0, with_e2e=True):
+    """Times `steps` fused-mixer calls on workload `name`.  Returns a dict of rank-reduced results."""
+    from qwengine_b200 import api
+    w = build_workload(name, world, rank, args.seed)
+    mx = api.Mixer(w["n_seq"], w["n_new"], kv_heads=w["kv_heads"])
+    mx.bind(w["q"], w["kc"], w["vc"], w["pos"], w["out"], k_new=w["k_new"], v_new=w["v_new"], gate=w["gate"],
+            lse=w["lse"], cache_row=w["cache_row"], flags=api.F_ROPE | api.F_APPEND | api.F_GATE | flags_extra)
+    api.profile_enable(True)
+    steps = args.steps if w["n_new"] < 64 else max(3, min(args.steps, 20))
+    warm = max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warm):
+        mx.forward()
+    barrier()
+    mx.check_status()
+    launches = mx.launches()
+
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    barrier()
+    ev[0].record()
+    for _ in range(steps):
+        mx.forward()
+    ev[1].record()
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[1])
+    kernel_ms = []
+    for _ in range(steps):  # dominant-kernel time: an event pair around that kernel alone, every step
+        mx.forward()
+        kernel_ms.append(api.profile_last_kernel_ms())
+    barrier()
+
+    e2e_ms, h2d, d2h = None, 0, 0
+    if with_e2e:
+        names = ("q", "k_new", "v_new", "gate")
+        host_in = {k: w[k].cpu().pin_memory() for k in names}
+        host_pos = w["pos"].cpu().pin_memory()
+        host_out = torch.empty(w["out"].shape, dtype=w["out"].dtype).pin_memory()
+        h2d = sum(t.numel() * t.element_size() for t in host_in.values()) + host_pos.numel() * 4
+        d2h = host_out.numel() * host_out.element_size()
+
+        def e2e_step():
+            for k in names:
+                w[k].copy_(host_in[k], non_blocking=True)
+            w["pos"].copy_(host_pos, non_blocking=True)
+            mx.forward()
+            host_out.copy_(w["out"], non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev2[0].record()
+        for _ in range(steps):
+            e2e_step()
+        ev2[1].record()
+        barrier()
+        e2e_ms = ev2[0].elapsed_time(ev2[1])
+    mx.check_status()
+
+    stats = torch.tensor([total_ms, e2e_ms or 0.0, float(np.mean(kernel_ms))], device="cuda", dtype=torch.float64)
+    sums = torch.tensor([w["kv_bytes"], w["flops"]], device="cuda", dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(stats, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.all_reduce(sums, op=torch.distributed.ReduceOp.SUM)
+    total_ms, e2e_ms, k_ms = [float(x) for x in stats.cpu()]
+    kv_all, flops_all = [float(x) for x in sums.cpu()]
+    return {"w": w, "steps": steps, "warmup": warm, "ms_per_step": total_ms / steps, "e2e_ms_per_step": e2e_ms / steps,
+            "kernel_ms": k_ms, "kv_bytes_all": kv_all, "flops_all": flops_all, "launches": launches * steps,
+            "h2d": h2d, "d2h": d2h}
+
+
+def describe(name, world, w):
+    _, n_new, hist = WORKLOADS[name]
+    return ("%s: %d seq(s) x %d new token(s), kv history %s, 24q/4kv heads, head_dim 256, partial RoPE 64, "
+            "sigmoid gate" % (name, w["n_seq_global"], n_new, hist))
+
+
+SHARDING = {1: "none", 2: "kv-head (2 per GPU)", 4: "kv-head (1 per GPU)", 8: "kv-head x 2-way sequence split"}
+
+
+def hbm_line(name, r, world, peaks):
+    hbm_peak, _, kind = peaks
+    w = r["w"]
+    achieved = w["kv_bytes"] / (r["kernel_ms"] * 1e-3) / 1e9
+    return {
+        "metric": "decode_attn_kv_GBps", "value": round(r["kv_bytes_all"] / (r["ms_per_step"] * 1e-3) / 1e9, 1),
+        "unit": "GB/s", "n_gpus": world, "steps": r["steps"], "warmup": r["warmup"],
+        "ms_per_step": round(r["ms_per_step"], 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded N(0,1) bf16 q/k/v/gate and KV cache, no dataset",
+        "config": {"workload": describe(name, world, w), "sharding": SHARDING[world],
+                   "l2_policy": "inputs larger than L2: %.0f MB of KV per GPU per step vs 126 MB L2" % (w["kv_bytes"] / 1e6)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
+                     "frac": round(achieved / hbm_peak, 4), "traffic": None, "peak_kind": kind,
+                     "kernel": "splitkv_kernel", "kernel_ms": round(r["kernel_ms"], 5)},
+        "e2e": {"value": round(r["kv_bytes_all"] / (r["e2e_ms_per_step"] * 1e-3) / 1e9, 1), "unit": "GB/s",
+                "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
+        "gpu_launches": r["launches"],
+    }
+
+
+def tensor_line(name, r, world, peaks, mode):
+    _, tc_peak, kind = peaks
+    w = r["w"]
+    achieved = w["flops"] / (r["kernel_ms"] * 1e-3) / 1e12
+    return {
+        "metric": "prefill_attn_TFLOPs", "value": round(r["flops_all"] / (r["ms_per_step"] * 1e-3) / 1e12, 1),
+        "unit": "TFLOP/s", "n_gpus": world, "steps": r["steps"], "warmup": r["warmup"],
+        "ms_per_step": round(r["ms_per_step"], 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded N(0,1) bf16 q/k/v/gate, no dataset",
+        "config": {"workload": describe(name, world, w), "sharding": SHARDING[world], "p_operand": mode,
+                   "l2_policy": "L2 flushed by the q/gate/out streams of the step (%.0f MB) plus KV"
+                                % (3 * w["q"].numel() * 2 / 1e6)},
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": tc_peak, "unit": "TFLOP/s",
+                     "frac": round(achieved / tc_peak, 4), "traffic": None, "peak_kind": kind,
+                     "kernel": "prefill_umma_kernel", "kernel_ms": round(r["kernel_ms"], 5),
+                     "flops_counted": "4*256*24 per unmasked (query,key) pair; the bf16 lo pass of P is not counted"},
+        "e2e": {"value": round(r["flops_all"] / (r["e2e_ms_per_step"] * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
+        "gpu_launches": r["launches"],
+    }
+
+
+def cpu_baseline(w, min_seconds=8.0):
+    """The CPU oracle timed on a bounded sample of the same workload: whole sequences of the batch,
+    repeated until `min_seconds` of CPU work have been done."""
+    from oracle import pyoracle as O
+    n = min(4, w["n_seq"])
+    hist = w["hist"][:n]
+    cap = hist.astype(np.int64) + w["n_new"]
+    rows = int(cap.sum())
+    f = lambda t: t.float().cpu().numpy()
+    kc = w["kc"][:rows].view(torch.int16).cpu().numpy().view(np.uint16)
+    vc = w["vc"][:rows].view(torch.int16).cpu().numpy().view(np.uint16)
+    cache_row = np.concatenate([[0], np.cumsum(cap)[:-1]])
+    q, k, v, g = f(w["q"][:n]), f(w["k_new"][:n]), f(w["v_new"][:n]), f(w["gate"][:n])
+    passes, t0 = 0, time.perf_counter()
+    while True:
+        O.mixer(q, k, v, g, kc, vc, hist, cache_row, kv_heads=w["kv_heads"])
+        passes += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds or passes >= 200:
+            break
+    nbytes = float(cap.sum()) * KV_BYTES_PER_TOKEN * w["kv_heads"] / 4 * passes
+    return {"value": round(nbytes / dt / 1e9, 4), "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+            "sample": "%d of %d sequences of the same batch, %d passes, %.1f s" % (n, w["n_seq"], passes, dt)}
 
 
 def run_ours(args, rank, local_rank, world):
@@ -142,125 +304,32 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    hbm_peak, tc_peak, peak_kind = measured_peaks()
-    w = build_decode_workload(args.workload, world, rank, args.seed)
-    mx = api.Mixer(w["n_seq"], w["n_new"], kv_heads=w["kv_heads"])
-    mx.bind(w["q"], w["kc"], w["vc"], w["pos"], w["out"], k_new=w["k_new"], v_new=w["v_new"], gate=w["gate"],
-            lse=w["lse"], cache_row=w["cache_row"])
-    api.profile_enable(True)
-
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        mx.forward()
-    barrier()
-    mx.check_status()
-    launches_per_step = mx.launches()
-
-    # ---- timed region 1: device-resident inputs -------------------------------------------------
+    peaks = measured_peaks()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    kernel_ms = []
-    barrier()
-    ev[0].record()
-    for _ in range(args.steps):
-        mx.forward()
-    ev[1].record()
-    barrier()
-    total_ms = ev[0].elapsed_time(ev[1])
-    # dominant-kernel time, one event pair per step around the split-KV kernel itself
-    for _ in range(args.steps):
-        mx.forward()
-        kernel_ms.append(api.profile_last_kernel_ms())
-    barrier()
-
-    # ---- timed region 2: end to end through the public call with host buffers -------------------
-    names = ("q", "k_new", "v_new", "gate")
-    host_in = {k: w[k].cpu().pin_memory() for k in names}
-    host_pos = w["pos"].cpu().pin_memory()
-    host_out = torch.empty(w["out"].shape, dtype=w["out"].dtype).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host_in.values()) + host_pos.numel() * 4
-    d2h = host_out.numel() * host_out.element_size()
-
-    def e2e_step():
-        for k in names:
-            w[k].copy_(host_in[k], non_blocking=True)
-        w["pos"].copy_(host_pos, non_blocking=True)
-        mx.forward()
-        host_out.copy_(w["out"], non_blocking=True)
-
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    ev2[0].record()
-    for _ in range(args.steps):
-        e2e_step()
-    ev2[1].record()
-    barrier()
-    e2e_ms = ev2[0].elapsed_time(ev2[1])
-    clocks = sampler.stop() if rank == 0 else None
-
-    # ---- reduce over ranks ---------------------------------------------------------------------------
-    stats = torch.tensor([total_ms, e2e_ms, float(np.mean(kernel_ms))], device="cuda", dtype=torch.float64)
-    sums = torch.tensor([w["kv_bytes"], w["flops"]], device="cuda", dtype=torch.float64)
+    if args.workload in ("decode", "verify"):
+        r = measure(args.workload, args, rank, world)
+        line = hbm_line(args.workload, r, world, peaks) if rank == 0 else None
+        if args.workload == "decode" and not args.no_prefill:
+            rp = measure("prefill8k", args, rank, world)
+            rf = measure("prefill8k", args, rank, world, flags_extra=api.F_FAST_P, with_e2e=False)
+            if rank == 0:
+                line["prefill"] = tensor_line("prefill8k", rp, world, peaks, "bf16 hi+lo pair (meets rel-L2 1e-3)")
+                fast = tensor_line("prefill8k", rf, world, peaks, "single bf16 (rel-L2 ~1.4e-3)")
+                line["prefill"]["fast_p"] = {"value": fast["value"], "unit": "TFLOP/s", "ms_per_step": fast["ms_per_step"],
+                                             "roofline_frac": fast["roofline"]["frac"]}
+    else:
+        r = measure(args.workload, args, rank, world, flags_extra=api.F_FAST_P if args.fast_p else 0)
+        line = tensor_line(args.workload, r, world, peaks,
+                           "single bf16" if args.fast_p else "bf16 hi+lo pair") if rank == 0 else None
+    if rank == 0:
+        line["clocks"] = sampler.stop()
+        if world == 1 and not args.no_cpu_baseline and args.workload in ("decode", "verify"):
+            line["cpu_baseline"] = cpu_baseline(r["w"])
+        print(json.dumps(line))
     if world > 1:
-        torch.distributed.all_reduce(stats, op=torch.distributed.ReduceOp.MAX)
-        torch.distributed.all_reduce(sums, op=torch.distributed.ReduceOp.SUM)
-    total_ms, e2e_ms, k_ms = [float(x) for x in stats.cpu()]
-    kv_bytes_all, flops_all = [float(x) for x in sums.cpu()]
-    if rank != 0:
-        return
-    ms_per_step = total_ms / args.steps
-    value = kv_bytes_all / (ms_per_step * 1e-3) / 1e9
-    achieved = w["kv_bytes"] / (k_ms * 1e-3) / 1e9
-    line = {
-        "metric": "decode_attn_kv_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic: seeded N(0,1) bf16 q/k/v/gate and KV cache, no dataset",
-        "config": {"workload": "%s: %d seqs x %d query token(s), kv history %s, 24q/4kv heads, head_dim 256, "
-                               "partial RoPE 64, sigmoid gate" % (args.workload, (16 if args.workload == "decode" else 8) * world, w["n_new"],
-                                                             "8192" if args.workload == "decode" else "U[2048,32768]"),
-                   "sharding": {1: "none", 2: "kv-head (2 per GPU)", 4: "kv-head (1 per GPU)",
-                                8: "kv-head x 2-way sequence split"}[world],
-                   "l2_policy": "inputs larger than L2: %.0f MB of KV per GPU per step vs 126 MB L2" % (w["kv_bytes"] / 1e6)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
-                     "frac": round(achieved / hbm_peak, 4), "traffic": None, "peak_kind": peak_kind,
-                     "kernel": "splitkv_kernel", "kernel_ms": round(k_ms, 5)},
-        "e2e": {"value": round(kv_bytes_all / (e2e_ms / args.steps * 1e-3) / 1e9, 1), "unit": "GB/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches_per_step * args.steps,
-        "clocks": clocks,
-    }
-    if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(w, args)
-    print(json.dumps(line))
-
-
-def cpu_baseline(w, args, max_seqs=4):
-    """The CPU oracle timed on a bounded sample of the same workload (first sequences of the batch)."""
-    from oracle import pyoracle as O
-    n = min(max_seqs, w["n_seq"])
-    hist = w["hist"][:n]
-    rows = int((hist.astype(np.int64) + w["n_new"]).sum())
-    f = lambda t: t.float().cpu().numpy()
-    kc = w["kc"][:rows].view(torch.int16).cpu().numpy().view(np.uint16)
-    vc = w["vc"][:rows].view(torch.int16).cpu().numpy().view(np.uint16)
-    cap = hist.astype(np.int64) + w["n_new"]
-    cache_row = np.concatenate([[0], np.cumsum(cap)[:-1]])
-    t0 = time.perf_counter()
-    O.mixer(f(w["q"][:n]), f(w["k_new"][:n]), f(w["v_new"][:n]), f(w["gate"][:n]), kc, vc, hist, cache_row,
-            kv_heads=w["kv_heads"])
-    dt = time.perf_counter() - t0
-    nbytes = float(cap.sum()) * KV_BYTES_PER_TOKEN * w["kv_heads"] / 4
-    return {"value": round(nbytes / dt / 1e9, 4), "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
-            "sample": "first %d of %d sequences of the same batch, one pass, %.2f s" % (n, w["n_seq"], dt)}
+        torch.distributed.destroy_process_group()
 
 
 def main():
@@ -269,20 +338,20 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "verify"])
+    ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS))
     ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--fast-p", action="store_true", help="prefill workloads: single-bf16 P operand")
+    ap.add_argument("--no-prefill", action="store_true", help="decode workload: skip the prefill8k sub-measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
-    if world != args.gpus and world == 1 and args.gpus > 1:
+    if world == 1 and args.gpus > 1:
         raise SystemExit("launch with torchrun --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus))
     if args.impl == "reference":
         from bench_reference import run_reference
         run_reference(args, rank, local_rank, world)
         return
     run_ours(args, rank, local_rank, world)
-    if world > 1:
-        torch.distributed.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -133,9 +133,9 @@ struct AttnCall {
 int splitkv_rb(int n_new) { return n_new < 5 ? n_new : 5; }  // tokens per unit: <= 30 rows = two 16-row tiles
 size_t splitkv_slot_floats(int rb) { return (size_t)rb * GROUP * PART_STRIDE; }
 
-template <int MT, int DS, int STAGES, typename TIn, typename TOut>
+template <int MT, int DS, int STAGES, int LOK, typename TIn, typename TOut>
 int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, cudaStream_t st) {
-  auto kern = splitkv_kernel<MT, DS, STAGES, TIn, TOut>;
+  auto kern = splitkv_kernel<MT, DS, STAGES, LOK, TIn, TOut>;
   constexpr size_t smem = splitkv_smem_bytes<MT, DS, STAGES>();
   static bool configured[64] = {false};
   int dev = 0;
@@ -152,6 +152,19 @@ int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKV
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
   splitkv_merge_kernel<TOut><<<n_units, 256, 0, st>>>(p);
   return check_launch("splitkv_merge_kernel");
+}
+
+// Picks the instantiation: fp32 queries carry a bf16 "lo" part on all 256 channels (16 k-steps),
+// bf16 queries only on the 64 rotated ones (4 k-steps) and none when they arrive rotated.
+template <int MT, int STAGES>
+int launch_splitkv_mt(const AttnCall &c, const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p,
+                      cudaStream_t st) {
+  if (c.q_is_f32) return launch_splitkv_t<MT, 2, STAGES, 16, float, float>(mk, mv, p, st);
+  if (c.out_is_f32)
+    return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, float>(mk, mv, p, st)
+                     : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, float>(mk, mv, p, st);
+  return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, uint16_t>(mk, mv, p, st)
+                   : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, uint16_t>(mk, mv, p, st);
 }
 
 int launch_splitkv(const AttnCall &c, cudaStream_t st) {
@@ -182,14 +195,7 @@ int launch_splitkv(const AttnCall &c, cudaStream_t st) {
   if (rc) return rc;
 
   const int mt = (p.rb * GROUP + 15) / 16;
-  if (mt == 1) {
-    if (c.q_is_f32) return launch_splitkv_t<1, 2, 3, float, float>(mk, mv, p, st);
-    if (c.out_is_f32) return launch_splitkv_t<1, 2, 3, uint16_t, float>(mk, mv, p, st);
-    return launch_splitkv_t<1, 2, 3, uint16_t, uint16_t>(mk, mv, p, st);
-  }
-  if (c.q_is_f32) return launch_splitkv_t<2, 2, 3, float, float>(mk, mv, p, st);
-  if (c.out_is_f32) return launch_splitkv_t<2, 2, 3, uint16_t, float>(mk, mv, p, st);
-  return launch_splitkv_t<2, 2, 3, uint16_t, uint16_t>(mk, mv, p, st);
+  return mt == 1 ? launch_splitkv_mt<1, 3>(c, mk, mv, p, st) : launch_splitkv_mt<2, 3>(c, mk, mv, p, st);
 }
 
 size_t splitkv_ws_floats(int n_seq, int n_new, int kv_heads) {
@@ -232,6 +238,7 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
     pc.q_heads = d->q_heads; pc.kv_heads = d->kv_heads; pc.scale = d->scale;
     pc.do_rope = (d->flags & QW_F_ROPE) != 0; pc.status = d->status;
     pc.rope = tab;
+    pc.fast_p = (d->flags & QW_F_FAST_P) ? 1 : 0;
     int n = 0;
     prof_mark(0, st);
     int rc = launch_prefill_umma(pc, st, &n);

@@ -19,6 +19,7 @@ struct PrefillCall {
   int n_seq, n_new, q_heads, kv_heads;
   float scale;
   bool do_rope;
+  int fast_p;            // 1: single bf16 P (faster, rel-L2 ~1.4e-3); 0: bf16 hi + lo pair
   int *status;
   RopeTable rope;
 };

@@ -133,7 +133,7 @@ __device__ __forceinline__ uint32_t q_hi_off(int row, int d) {
   return (uint32_t)(row * 512 + ((c16 ^ (row & 7)) << 4) + ((d & 7) << 1));
 }
 
-template <int MT, int DS, int STAGES, typename TIn, typename TOut>
+template <int MT, int DS, int STAGES, int LOK, typename TIn, typename TOut>
 __global__ void __launch_bounds__((SK_KS * DS + 1) * 32, 1)
 splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                const __grid_constant__ SplitKVParams p) {
@@ -221,8 +221,25 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   int u = (int)seg[2];
   long long pre = seg[1];
   const uint32_t qhi_s = smem_u32(qregion);
-  const uint32_t qlo_s = qhi_s + ROWS * 512;
-  const int n_lo_k = p.q_lo_dims / 16;
+  // Per-lane ldmatrix addresses.  The swizzle XORs the 16-byte column (d / 8) & 7 with row & 7,
+  // so for a fixed lane only four distinct column offsets occur; the rest is a constant stride.
+  uint32_t klane[4], vlane[4], qlane[MT][4];
+  {
+    const int krow = ks * 16 + (lane & 7) + ((lane >> 4) << 3);  // K: matrices (keys lo/hi) x (d lo/hi)
+    const int kc_sel = (lane >> 3) & 1;
+    const int vrow = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);  // V (transposed load)
+    const int vc_sel = lane >> 4;
+    const int arow = (lane & 7) + (((lane >> 3) & 1) << 3);  // Q: A-fragment row within 16
+    const int ac_sel = lane >> 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      klane[j] = krow * 128 + (((j * 2 + kc_sel) ^ (krow & 7)) << 4);
+      vlane[j] = (ds * DW / 64) * (SK_TK * 128) + vrow * 128 + (((j * 2 + vc_sel) ^ (vrow & 7)) << 4);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+        qlane[mt][j] = qhi_s + (mt * 16 + arow) * 512 + (((j * 2 + ac_sel) ^ (arow & 7)) << 4);
+    }
+  }
 
   while (pre < g1 && u < n_units) {
     const UnitInfo ui = unit_info(p, u);
@@ -325,18 +342,17 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
 #pragma unroll
             for (int j = 0; j < 4; ++j) { s[mt][n][j] = 0.f; s2[mt][n][j] = 0.f; }
 
-        const int krow = ks * 16 + (lane & 7) + ((lane >> 4) << 3);  // ldmatrix row address: key
-        const int kc_sel = (lane >> 3) & 1;                          // which 8-wide d half
-        const int arow = (lane & 7) + (((lane >> 3) & 1) << 3);      // A-fragment row within 16
-        const int ac_sel = lane >> 4;
-#pragma unroll 4
+        uint32_t kb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) kb[j] = kbase + klane[j];
+#pragma unroll
         for (int kk = 0; kk < 16; ++kk) {
           uint32_t b0, b1, b2, b3;
-          ldsm_x4(kbase + kv_tile_off<SK_TK>(krow, kk * 16 + kc_sel * 8), b0, b1, b2, b3);
+          ldsm_x4(kb[kk & 3] + (kk >> 2) * (SK_TK * 128), b0, b1, b2, b3);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             uint32_t a0, a1, a2, a3;
-            ldsm_x4(qhi_s + q_hi_off(mt * 16 + arow, kk * 16 + ac_sel * 8), a0, a1, a2, a3);
+            ldsm_x4(qlane[mt][kk & 3] + (kk >> 2) * 128, a0, a1, a2, a3);
             if (kk & 1) {
               mma_bf16_16816(s2[mt][0], a0, a1, a2, a3, b0, b1);
               mma_bf16_16816(s2[mt][1], a0, a1, a2, a3, b2, b3);
@@ -344,17 +360,16 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
               mma_bf16_16816(s[mt][0], a0, a1, a2, a3, b0, b1);
               mma_bf16_16816(s[mt][1], a0, a1, a2, a3, b2, b3);
             }
-          }
-        }
-        for (int kk = 0; kk < n_lo_k; ++kk) {
-          uint32_t b0, b1, b2, b3;
-          ldsm_x4(kbase + kv_tile_off<SK_TK>(krow, kk * 16 + kc_sel * 8), b0, b1, b2, b3);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            uint32_t a0, a1, a2, a3;
-            ldsm_x4(qlo_s + q_hi_off(mt * 16 + arow, kk * 16 + ac_sel * 8), a0, a1, a2, a3);
-            mma_bf16_16816(s2[mt][0], a0, a1, a2, a3, b0, b1);
-            mma_bf16_16816(s2[mt][1], a0, a1, a2, a3, b2, b3);
+            if (kk < LOK) {  // the bf16 "lo" part of Q against the same K fragment
+              ldsm_x4(qlane[mt][kk & 3] + (kk >> 2) * 128 + ROWS * 512, a0, a1, a2, a3);
+              if (kk & 1) {
+                mma_bf16_16816(s[mt][0], a0, a1, a2, a3, b0, b1);
+                mma_bf16_16816(s[mt][1], a0, a1, a2, a3, b2, b3);
+              } else {
+                mma_bf16_16816(s2[mt][0], a0, a1, a2, a3, b0, b1);
+                mma_bf16_16816(s2[mt][1], a0, a1, a2, a3, b2, b3);
+              }
+            }
           }
         }
 
@@ -415,12 +430,13 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         }
 
         // O += P V on this warp's 16 keys and DW output channels
-        const int vrow = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-        const int vc_sel = lane >> 4;
+        uint32_t vb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) vb[j] = vbase + vlane[j];
 #pragma unroll
         for (int n2 = 0; n2 < NT_O / 2; ++n2) {
           uint32_t v0, v1, v2, v3;
-          ldsm_x4_trans(vbase + kv_tile_off<SK_TK>(vrow, ds * DW + n2 * 16 + vc_sel * 8), v0, v1, v2, v3);
+          ldsm_x4_trans(vb[n2 & 3] + (n2 >> 2) * (SK_TK * 128), v0, v1, v2, v3);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             mma_bf16_16816(o[mt][2 * n2], phi[mt][0], phi[mt][1], phi[mt][2], phi[mt][3], v0, v1);

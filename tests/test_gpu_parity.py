@@ -145,6 +145,58 @@ def test_prefill_chunk_splitkv(hist, T):
     check_lse(lse, lse_ref, "prefill splitkv")
 
 
+# ---- prefill on the tcgen05 kernel (chunks of >= 64 rows) -------------------------------------------------
+@pytest.mark.parametrize("hist,T,kvh", [([0], 128, 1), ([0], 64, 2), ([0], 256, 1), ([100], 200, 2), ([37], 333, 1),
+                                        ([500, 3], 96, 1), ([0], 512, 4), ([1000], 128, 4)])
+def test_prefill_umma(hist, T, kvh):
+    c = Case(55 + T, hist, T, kv_heads=kvh)
+    ref, lse_ref, kc_ref, vc_ref = c.oracle()
+    o32, lse, kc, vc, mx = run_case(c, out_f32=True)
+    assert mx.launches() == 2, "expected rope_append + the tcgen05 kernel"
+    assert np.array_equal(kc, kc_ref) and np.array_equal(vc, vc_ref)
+    check_out(o32, ref, "prefill umma")
+    check_lse(lse, lse_ref, "prefill umma")
+    o16, _, _, _, _ = run_case(c, out_f32=False)
+    check_out_bf16(o16, ref, "prefill umma bf16")
+
+
+def test_prefill_umma_mrope_and_stale_rows():
+    c = Case(58, [70], 130, kv_heads=1, mrope=True, pad_rows=200)
+    c.kc0[c.kc0 == 0x4F00] = 0x7FC0
+    c.vc0[c.vc0 == 0x4F00] = 0x7FC0
+    ref, lse_ref, kc_ref, _ = c.oracle()
+    o32, lse, kc, _, _ = run_case(c, out_f32=True)
+    n = (70 + 130) * 256
+    assert np.array_equal(kc.reshape(-1)[:n], kc_ref.reshape(-1)[:n])
+    assert np.isfinite(o32).all()
+    check_out(o32, ref, "prefill umma mrope")
+    check_lse(lse, lse_ref, "prefill umma mrope")
+
+
+def test_chunked_prefill_equals_single_shot_gpu():
+    """Config 4 in miniature: 4 chunks of 128 appended to the cache equal one 512-token shot."""
+    c = Case(59, [0], 512, kv_heads=1)
+    o_full, lse_full, kc_full, vc_full, _ = run_case(c, out_f32=True)
+    mx = api.Mixer(1, 128, kv_heads=1)
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    outs = []
+    for t0 in range(0, 512, 128):
+        sl = slice(t0, t0 + 128)
+        out = torch.empty(1, 128, 6, 256, dtype=torch.float32, device="cuda")
+        pos.fill_(t0)
+        mx.bind(dev_bf16(c.q[:, sl]), kc, vc, pos, out, k_new=dev_bf16(c.k[:, sl]), v_new=dev_bf16(c.v[:, sl]),
+                gate=dev_bf16(c.gate[:, sl]))
+        mx.forward()
+        torch.cuda.synchronize()
+        mx.check_status()
+        outs.append(host_f32(out).reshape(128, 6, 256))
+    got = np.concatenate(outs)
+    assert np.array_equal(host_bits(kc), kc_full)
+    # same kernel, same tile order per row => identical bits
+    assert np.array_equal(got, o_full)
+
+
 # ---- drop-in launchers with the reference's argument lists ------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("B", [1, 4, 8])
