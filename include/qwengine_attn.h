@@ -43,7 +43,8 @@ enum {
   QW_ERR_SHAPE = 2,     /* geometry outside the supported set                     */
   QW_ERR_CUDA = 3,      /* a CUDA runtime / driver call failed                    */
   QW_ERR_WORKSPACE = 4, /* scratch / workspace too small                          */
-  QW_ERR_DEVICE = 5     /* a kernel recorded an error (bounded wait ran out)      */
+  QW_ERR_DEVICE = 5,    /* a kernel recorded an error (bounded wait ran out)      */
+  QW_ERR_TOO_LARGE = 6  /* request exceeds a fixed built-in capacity              */
 };
 
 /* Human-readable text for a QW_ERR_* code. */
@@ -88,6 +89,25 @@ int qw_attn_decode_f32(const float *q, const qw_bf16 *kc, const qw_bf16 *vc, flo
                        const int *dpos, int dim, int kv_heads, int q_heads, float scale,
                        float *scratch, int ctx, int B, qw_stream stream);
 size_t qw_attn_decode_scratch_floats(int q_heads, int kv_heads, int ctx, int B);
+
+/* Decode / verify attention for callers that cannot hand over scratch memory.
+ * No counterpart in the reference, whose call sites always pass their own `scores` buffer.
+ * Some hosts of this library may not allocate device memory at the point where they launch
+ * attention: an engine that takes all of its device memory in one block at start-up and has
+ * nothing left to carve a workspace from, a plugin slot that is given tensors but no allocator,
+ * or a latency-critical loop where a cudaMalloc (which can synchronise the device) is banned.
+ * This variant of qw_attn_decode_bf16 takes no scratch argument: the split-KV partials go to
+ * a fixed array that lives inside the library image, 5.2 MB of device memory that every GPU
+ * which loads the library keeps until the process exits.  Limits: B <= 8 and kv_heads <= 4;
+ * anything larger returns QW_ERR_TOO_LARGE.  It calls no cudaMalloc, cudaFree or other
+ * allocating routine.  The first call on each device looks the array's device address up
+ * (cudaGetSymbolAddress) and remembers it; make that first call outside any stream capture.
+ * All calls on a device share the one array and leave their partials in it; nothing in it has
+ * to be cleared between calls, but two calls whose kernels overlap on the GPU (different
+ * streams, or concurrent graph branches) race on it -- serialise them. */
+int qw_attn_decode_bf16_noalloc(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out,
+                                const int *dpos, int dim, int kv_heads, int q_heads, float scale,
+                                int ctx, int B, qw_stream stream);
 
 /* Chunked-prefill attention: row t of q[T][q_heads][dim] attends to the first
  * *dpos + t + 1 cache rows.  `scratch` (reference: T * q_heads * ctx floats) is used

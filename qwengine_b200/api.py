@@ -48,6 +48,7 @@ _SIGS = {
     "qw_kv_append_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "qw_attn_decode_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp]),
     "qw_attn_decode_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp]),
+    "qw_attn_decode_bf16_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp]),
     "qw_attn_decode_scratch_floats": (C.c_size_t, [_i, _i, _i, _i]),
     "qw_attn_prefill_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp]),
     "qw_attn_prefill_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _i, _i, _vp]),
@@ -117,6 +118,13 @@ def kv_append(k, v, kc, vc, dpos, kvdim, B=1, stream=None):
 def attn_decode(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, scratch, ctx, B=1, stream=None):
     _check(getattr(lib(), "qw_attn_decode_" + _suffix(q))(
         _p(q), _p(kc), _p(vc), _p(out), _p(dpos), dim, kv_heads, q_heads, scale, _p(scratch), ctx, B, _stream(stream)))
+
+
+def attn_decode_noalloc(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, ctx, B=1, stream=None):
+    """attn_decode without a scratch argument: partials go to an array built into the library
+    (bf16 only, B <= 8).  The first call on a device must happen outside stream capture."""
+    _check(lib().qw_attn_decode_bf16_noalloc(_p(q), _p(kc), _p(vc), _p(out), _p(dpos), dim, kv_heads, q_heads, scale,
+                                             ctx, B, _stream(stream)))
 
 
 def attn_prefill(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, scratch, ctx, T, stream=None):

@@ -283,6 +283,33 @@ int attn_dropin(const T *q, const qw_bf16 *kc, const qw_bf16 *vc, T *out, const 
   return launch_splitkv(c, st);
 }
 
+// ---- allocation-free decode: split-KV partials in a fixed array inside the library image --------
+// Sized for the largest request the entry point accepts: B <= 8 tokens (two unit blocks of <= 5)
+// and kv_heads <= 4 give at most 8 units; up to 160 CTAs; one slot = 5 tokens x 6 heads x 260 floats.
+constexpr int NOALLOC_MAX_B = 8;
+constexpr int NOALLOC_MAX_KV_HEADS = 4;
+constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)(160 + 2 * NOALLOC_MAX_KV_HEADS) * 5 * GROUP * PART_STRIDE;
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+
+// In host code the name g_noalloc_scratch is only a handle for the symbol, not an address a kernel
+// could use.  The device address is looked up once per device, with that device current.
+int noalloc_scratch_address(float **out) {
+  static std::mutex mu;
+  static float *addr[64] = {nullptr};
+  int dev = 0;
+  QW_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return QW_ERR_ARG;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void *p = nullptr;
+    QW_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    if (!p) return QW_ERR_CUDA;
+    addr[dev] = static_cast<float *>(p);
+  }
+  *out = addr[dev];
+  return QW_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -295,6 +322,7 @@ const char *qw_strerror(int code) {
     case QW_ERR_CUDA: return "a CUDA call failed (see qw_last_cuda_error)";
     case QW_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
     case QW_ERR_DEVICE: return "a kernel reported an error through the status word";
+    case QW_ERR_TOO_LARGE: return "request exceeds a fixed built-in capacity (allocation-free decode: B <= 8, kv_heads <= 4)";
     default: return "unknown error code";
   }
 }
@@ -402,6 +430,26 @@ int qw_attn_decode_f32(const float *q, const qw_bf16 *kc, const qw_bf16 *vc, flo
   return attn_dropin<float>(q, kc, vc, out, dpos, dim, kv_heads, q_heads, scale, scratch, ctx, B, true,
                             (cudaStream_t)stream);
 }
+int qw_attn_decode_bf16_noalloc(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out,
+                                const int *dpos, int dim, int kv_heads, int q_heads, float scale, int ctx, int B,
+                                qw_stream stream) {
+  g_launches = 0;
+  if (!q || !kc || !vc || !out || !dpos || ctx <= 0 || B < 0) return QW_ERR_ARG;
+  if (!geometry_ok(dim, kv_heads, q_heads)) return QW_ERR_SHAPE;
+  if (B > NOALLOC_MAX_B || kv_heads > NOALLOC_MAX_KV_HEADS) return QW_ERR_TOO_LARGE;
+  if (B == 0) return QW_OK;
+  float *scratch = nullptr;
+  int rc = noalloc_scratch_address(&scratch);
+  if (rc) return rc;
+  AttnCall c;
+  memset(&c, 0, sizeof(c));
+  c.q = q; c.out = out; c.kc = kc; c.vc = vc; c.cache_rows = ctx; c.pos = dpos;
+  c.n_seq = 1; c.n_new = B; c.q_heads = q_heads; c.kv_heads = kv_heads;
+  c.theta = 1e7f; c.scale = scale;
+  c.ws = scratch; c.ws_floats = NOALLOC_SCRATCH_FLOATS;
+  return launch_splitkv(c, (cudaStream_t)stream);
+}
+
 int qw_attn_prefill_bf16(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out, const int *dpos,
                          int dim, int kv_heads, int q_heads, float scale, float *scratch, int ctx, int T,
                          qw_stream stream) {
