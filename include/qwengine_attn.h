@@ -143,8 +143,13 @@ enum {
   QW_F_GATE = 4,       /* multiply the output by sigmoid(gate)                          */
   QW_F_OUT_F32 = 8,    /* `out` is float instead of bf16 (checking aid)                 */
   QW_F_NO_UMMA = 16,   /* force the split-KV kernel even for long prefill chunks        */
-  QW_F_FAST_P = 32     /* tcgen05 prefill only: feed P as one bf16 instead of a bf16 hi+lo
-                          pair; 1/3 less tensor work, output rel-L2 ~1.4e-3 instead of 6e-4 */
+  QW_F_FAST_P = 32,    /* tcgen05 prefill only: feed P as one bf16 instead of a bf16 hi+lo
+                          pair; 1/3 less tensor work, output rel-L2 ~1.4e-3 instead of 2e-6 */
+  QW_F_UMMA_1CTA = 64, /* tcgen05 prefill only: use the single-CTA kernel instead of the CTA-pair
+                          (cta_group::2) kernel                                            */
+  QW_F_NO_CAUSAL = 128 /* every row sees exactly pos[s] (>= 1) keys of its sequence: the call covers
+                          a KV sub-range that does not contain the new rows (cross-GPU KV split);
+                          excludes QW_F_APPEND, q must arrive rotated                       */
 };
 
 typedef struct qw_mixer_desc {

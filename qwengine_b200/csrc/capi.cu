@@ -124,7 +124,7 @@ struct AttnCall {
   const int *mpos;
   int n_seq, n_new, q_heads, kv_heads;
   float theta, scale;
-  bool do_rope, do_gate;
+  bool do_rope, do_gate, no_causal;
   float *ws;
   size_t ws_floats;
   int *status;
@@ -185,7 +185,7 @@ int launch_splitkv(const AttnCall &c, cudaStream_t st) {
   p.G = (int)G;
   p.q_lo_dims = c.q_is_f32 ? HEAD_DIM : (c.do_rope ? ROTARY_DIM : 0);
   p.scale_log2 = c.scale * LOG2E;
-  p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate;
+  p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate; p.no_causal = c.no_causal;
   p.rope = make_rope_table(c.theta, ROTARY_DIM);
 
   CUtensorMap mk, mv;
@@ -227,7 +227,9 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
     int rc = check_launch("rope_append_kernel");
     if (rc) return rc;
   }
-  const bool use_umma = !(d->flags & QW_F_NO_UMMA) && !partial && prefill_umma_supported(d->n_new);
+  if ((d->flags & QW_F_NO_CAUSAL) && (d->flags & QW_F_APPEND)) return QW_ERR_ARG;  // a sub-range call never owns the new rows
+  const bool use_umma =
+      !(d->flags & (QW_F_NO_UMMA | QW_F_NO_CAUSAL)) && !partial && prefill_umma_supported(d->n_new);
   if (use_umma) {
     PrefillCall pc;
     memset(&pc, 0, sizeof(pc));
@@ -241,7 +243,7 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
     pc.fast_p = (d->flags & QW_F_FAST_P) ? 1 : 0;
     int n = 0;
     prof_mark(0, st);
-    int rc = launch_prefill_umma(pc, st, &n);
+    int rc = (d->flags & QW_F_UMMA_1CTA) ? launch_prefill_umma(pc, st, &n) : launch_prefill_umma_pair(pc, st, &n);
     prof_mark(1, st);
     g_launches += n;
     if (rc == QW_ERR_CUDA) {
@@ -258,6 +260,7 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
   c.pos = d->pos; c.mpos = d->mpos; c.n_seq = d->n_seq; c.n_new = d->n_new;
   c.q_heads = d->q_heads; c.kv_heads = d->kv_heads; c.theta = d->theta; c.scale = d->scale;
   c.do_rope = (d->flags & QW_F_ROPE) != 0; c.do_gate = (d->flags & QW_F_GATE) != 0;
+  c.no_causal = (d->flags & QW_F_NO_CAUSAL) != 0;
   c.ws = reinterpret_cast<float *>(d->workspace); c.ws_floats = d->workspace_bytes / sizeof(float);
   c.status = d->status;
   if (!c.ws || (reinterpret_cast<uintptr_t>(c.ws) & 15)) return QW_ERR_WORKSPACE;
@@ -311,6 +314,17 @@ int noalloc_scratch_address(float **out) {
 }
 
 }  // namespace
+
+#ifdef QWB_TIMELINE
+namespace qwb {
+unsigned long long *g_timeline_buf = nullptr;
+int g_timeline_block = 0;
+}  // namespace qwb
+extern "C" void qw_debug_set_timeline(unsigned long long *buf, int block) {
+  qwb::g_timeline_buf = buf;
+  qwb::g_timeline_block = block;
+}
+#endif
 
 extern "C" {
 

@@ -133,8 +133,8 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 // Bounded wait: a short spin, then polling against the wall clock.  After WAIT_LIMIT_NS the
 // wait gives up and returns false; the caller records an error code and unwinds without
-// waiting again, so a lost signal costs a second, not the GPU.
-constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;
+// waiting again, so a lost signal costs a fraction of a second, not the GPU.
+constexpr uint64_t WAIT_LIMIT_NS = 200000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   for (int i = 0; i < 64; ++i)
     if (mbar_try_wait(bar, parity)) return true;

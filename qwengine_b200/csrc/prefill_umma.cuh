@@ -28,5 +28,7 @@ struct PrefillCall {
 bool prefill_umma_supported(int n_new);
 // Launches the kernel(s); *n_launched receives how many.  Returns a QW_* code.
 int launch_prefill_umma(const PrefillCall &c, cudaStream_t st, int *n_launched);
+// Same contract, CTA-pair kernel (tcgen05 cta_group::2); needs an even number of query heads.
+int launch_prefill_umma_pair(const PrefillCall &c, cudaStream_t st, int *n_launched);
 
 }  // namespace qwb

@@ -47,6 +47,7 @@ struct SplitKVParams {
   int q_lo_dims;          // 0, 64 or 256: leading dims that carry a bf16 "lo" part
   float scale_log2;       // softmax scale * log2(e)
   int do_rope, do_gate;
+  int no_causal;          // every row sees exactly pos[s] keys (a KV sub-range without the new rows)
   RopeTable rope;
 };
 
@@ -66,7 +67,7 @@ __device__ __forceinline__ UnitInfo unit_info(const SplitKVParams &p, int u) {
   ui.tok0 = ui.blk * p.rb;
   ui.ntok = min(p.rb, p.n_new - ui.tok0);
   ui.pos = p.pos[ui.s];
-  ui.len = ui.pos + ui.tok0 + ui.ntok;
+  ui.len = p.no_causal ? ui.pos : ui.pos + ui.tok0 + ui.ntok;
   return ui;
 }
 __device__ __forceinline__ int unit_tiles(const SplitKVParams &p, int u) {
@@ -309,14 +310,14 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         l_run[mt][h2] = 0.f;
         const int row = mt * 16 + h2 * 8 + qd;
         const int b = min(row / GROUP, ui.ntok - 1);
-        lim[mt][h2] = ui.pos + ui.tok0 + b + 1;  // keys visible to this row
+        lim[mt][h2] = p.no_causal ? ui.pos : ui.pos + ui.tok0 + b + 1;  // keys visible to this row
       }
 #pragma unroll
       for (int n = 0; n < NT_O; ++n)
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[mt][n][j] = 0.f;
     }
-    const int lim_min = ui.pos + ui.tok0 + 1;
+    const int lim_min = p.no_causal ? ui.pos : ui.pos + ui.tok0 + 1;
 
     for (int t = t0; t < t1; ++t, ++it) {
       const int st = it % STAGES;

@@ -1,0 +1,85 @@
+"""Host-side partitioning of the attention path across the GPUs of one box (one process per GPU).
+
+The reference is single-GPU; this is new design.  Three partitions are used:
+  * KV-head sharding (2 and 4 GPUs): a rank owns kv_heads/N KV heads and their 6x query heads of
+    every sequence; outputs are disjoint head slices and no data crosses GPUs.
+  * KV head x sequence split (8 GPUs): 4 KV heads x 2 groups of sequences.
+  * KV-range split of one long sequence across ranks: each rank attends to its sub-range and
+    produces (o, m, l) partials; the partials are all-gathered and merged in rank order.
+Functions here are pure host logic (lists, torch.distributed calls); they run on CPU with the gloo
+backend in the tests and with NCCL on the GPUs.
+"""
+import torch
+import torch.distributed as dist
+
+PARTIAL_FLOATS = 260
+
+
+def shard_plan(world, rank):
+    """(kv_heads_local, first_kv_head, seq_groups, seq_group) for KV-head sharding of 4 KV heads."""
+    if world == 1:
+        return 4, 0, 1, 0
+    if world == 2:
+        return 2, 2 * rank, 1, 0
+    if world == 4:
+        return 1, rank, 1, 0
+    if world == 8:
+        return 1, rank % 4, 2, rank // 4
+    raise ValueError("world size must be 1, 2, 4 or 8")
+
+
+def partition_by_kv_bytes(kv_lens, n_bins, max_share=None):
+    """Greedy longest-first assignment of sequences to bins by KV bytes (proportional to length).
+    A sequence longer than `max_share` (default: total / n_bins, rounded up to 64) is cut into
+    KV sub-ranges of at most that size first.  Returns a list of n_bins lists of
+    (seq, start, end) ranges; every token of every sequence appears exactly once."""
+    total = sum(int(x) for x in kv_lens)
+    if max_share is None:
+        max_share = -(-max(1, -(-total // n_bins)) // 64) * 64
+    pieces = []
+    for s, L in enumerate(kv_lens):
+        L = int(L)
+        a = 0
+        while L - a > max_share:
+            pieces.append((s, a, a + max_share))
+            a += max_share
+        if L > a:
+            pieces.append((s, a, L))
+    pieces.sort(key=lambda r: (-(r[2] - r[1]), r[0], r[1]))
+    bins, load = [[] for _ in range(n_bins)], [0] * n_bins
+    for pc in pieces:
+        b = min(range(n_bins), key=lambda i: (load[i], i))
+        bins[b].append(pc)
+        load[b] += pc[2] - pc[1]
+    for b in bins:
+        b.sort()
+    return bins
+
+
+def gather_partials(partial, group=None):
+    """All-gathers one rank's partials [rows, q_heads, 260] into [world, rows, q_heads, 260],
+    ordered by rank, which is also the order the merge uses (fixed => bit-stable)."""
+    world = dist.get_world_size(group)
+    partial = partial.contiguous()
+    out = torch.empty((world * partial.shape[0],) + tuple(partial.shape[1:]), dtype=partial.dtype,
+                      device=partial.device)
+    dist.all_gather_into_tensor(out, partial, group=group)
+    return out.view((world,) + tuple(partial.shape))
+
+
+def merge_partials_reference(parts):
+    """Merge [n_parts, rows, heads, 260] partials on the host (torch, any device), in index order.
+    The GPU path uses qw_combine_partials; this is its specification for the CPU tests.
+    Returns (o [rows, heads, 256] normalised, lse [rows, heads] natural log)."""
+    o, m, l = parts[..., :256], parts[..., 256], parts[..., 257]
+    live = l > 0
+    m_eff = torch.where(live, m, torch.full_like(m, float("-inf")))
+    mg = m_eff.max(dim=0).values
+    m_use = torch.where(torch.isinf(mg), torch.zeros_like(mg), mg)
+    f = torch.where(live, torch.exp2(m - m_use), torch.zeros_like(m))
+    lg = torch.zeros_like(mg)
+    acc = torch.zeros_like(o[0])
+    for k in range(parts.shape[0]):   # fixed order
+        lg = lg + l[k] * f[k]
+        acc = acc + o[k] * f[k][..., None]
+    return acc / lg[..., None], (mg + torch.log2(lg)) * 0.6931471805599453
