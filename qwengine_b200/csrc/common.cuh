@@ -72,7 +72,19 @@ __device__ __forceinline__ void rope_sincos_fast(int pos, double inv_freq, float
   sincosf((float)r, &s, &c);
 }
 
+// Cheapest form, for the tcgen05 prologue: the angle is formed and reduced to [-pi, pi] in double,
+// where the hardware sin/cos approximations are good to ~4e-7 absolute -- far below the 2^-17 that
+// the bf16 hi + lo pair of the rotated value keeps.
+__device__ __forceinline__ void rope_sincos_reduced(int pos, double inv_freq, float &c, float &s) {
+  const double a = (double)pos * inv_freq;
+  const double k = rint(a * 0.15915494309189535);
+  const float r = (float)fma(-k, 6.283185307179586, a);
+  __sincosf(r, &s, &c);
+}
+
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// Same value to ~2 ulp with the approximate reciprocal: for epilogues that are instruction-bound.
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -176,6 +176,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
   const int kv_len = pos + q0 + rows_valid;
   const int nt = (kv_len + P2_BN - 1) / P2_BN;
 
+  if (tid == 64) QWB_TL(27, 0);
   if (tid == 0) {
     mbar_init(&ctl->q_full, 1);
     mbar_init(&ctl->q_ready, 2 * P2_SM_THREADS);
@@ -399,7 +400,9 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
     const int qpos = pos + q0 + row;
     const uint32_t q_ready_addr = map_to_cta(smem_u32(&ctl->q_ready), 0);
     const uint32_t p_full_addr[2] = {map_to_cta(smem_u32(&ctl->p_full[0]), 0), map_to_cta(smem_u32(&ctl->p_full[1]), 0)};
+    if (tid == 64) QWB_TL(27, 1);
     bool ok = wait_or_abort(&ctl->q_full, 0, abort_flag);
+    if (tid == 64) QWB_TL(28, 0);
     if (ok && p.do_rope) {
       const size_t trow = (size_t)s * p.n_new + q0 + row;
       const bool live = row < rows_valid;
@@ -421,7 +424,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
           const float y = e ? bf16hi(yw[w2]) : bf16lo(yw[w2]);
           const int pz = (p.mpos && live) ? p.mpos[trow * 3 + mrope_component(i)] : qpos;
           float cs, sn;
-          rope_sincos_fast(pz, p.rope.inv_freq[i], cs, sn);
+          rope_sincos_reduced(pz, p.rope.inv_freq[i], cs, sn);
           xr[e] = x * cs - y * sn;
           yr[e] = x * sn + y * cs;
         }
@@ -437,6 +440,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
     }
     fence_proxy_async();
     remote_arrive_release(q_ready_addr);
+    if (tid == 64) QWB_TL(29, 0);
 
     float m_used = -INFINITY, l_run = 0.f;
     int o_seen = 0;  // P V completions observed so far, in order (tile t: o_done[t & 1], phase t / 2)
@@ -525,49 +529,81 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
       if (tid == 64) QWB_TL(9, j);
     }
 
+    if (tid == 64) QWB_TL(18, 0);
     ctl->lbuf[wg][row] = l_run;
     wait_pv_done(nt - 1);
+    if (tid == 64) QWB_TL(18, 1);
     asm volatile("bar.sync 1, %0;" ::"n"(P2_SM_THREADS) : "memory");
     if (!__all_sync(0xffffffffu, ok)) {
       if (lane == 0 && !*abort_flag && p.status) *p.status = DEV_ERR_SOFTMAX_WAIT;
       *abort_flag = 1;
     } else {
+      if (tid == 64) QWB_TL(18, 2);
       tc_fence_after();
       float l_tot = 0.f;
 #pragma unroll
       for (int w2 = 0; w2 < P2_NWG; ++w2) l_tot += ctl->lbuf[w2][row];
       const float inv = 1.f / l_tot;
       const size_t grow = ((size_t)s * p.n_new + q0 + row) * p.q_heads + head;
+      // O leaves TMEM one row per thread, but a row's 64 channels are one contiguous 128-byte
+      // run in `out` and `gate`.  Each warp therefore transposes its 32 rows x 64 channels through
+      // a padded staging area (Q and the K/V ring are idle by now: every MMA has retired) and then
+      // walks the rows with the lanes across the channels, two per lane: every gate load and every
+      // output store is one full coalesced line, and all 32 gate loads are in flight at once.
+      float *stage = reinterpret_cast<float *>(smem) + (warp - 2) * (32 * 65);
       const uint32_t t_o = tmem + lane_sel + TMEM_O + wg * 64;
+      const int row0 = (warp & 3) * 32;
+      const int nrows = min(32, rows_valid - row0);
+      const size_t elem0 = (((size_t)s * p.n_new + q0 + row0) * p.q_heads + head) * HEAD_DIM + wg * 64 + 2 * lane;
+      const size_t row_stride = (size_t)p.q_heads * HEAD_DIM;
+      if (tid == 64) QWB_TL(18, 3);
+      uint32_t gw[32];
+      {
+        const uint16_t *gp = p.gate ? p.gate + elem0 : nullptr;
+#pragma unroll
+        for (int rr = 0; rr < 32; ++rr) {
+          gw[rr] = (gp && rr < nrows) ? *reinterpret_cast<const uint32_t *>(gp) : 0u;
+          gp += gp ? row_stride : 0;
+        }
+      }
+      if (tid == 64) QWB_TL(18, 4);
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t orow[32];
         tmem_ld32(t_o + c * 32, orow);
         tmem_wait_ld();
-        if (row < rows_valid) {
-          const size_t off = grow * HEAD_DIM + wg * 64 + c * 32;
 #pragma unroll
-          for (int v8 = 0; v8 < 4; ++v8) {
-            float o8[8];
+        for (int i = 0; i < 32; ++i) stage[lane * 65 + c * 32 + i] = __uint_as_float(orow[i]) * inv;
+      }
+      __syncwarp();
+      if (tid == 64) QWB_TL(18, 5);
+      if (p.out_is_f32) {
+        float *op = reinterpret_cast<float *>(p.out) + elem0;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(orow[v8 * 8 + e]) * inv;
-            if (p.gate) {
-              float g8[8];
-              load8<uint16_t>(p.gate + off + v8 * 8, g8);
+        for (int rr = 0; rr < 32; ++rr, op += row_stride) {
+          if (rr < nrows) {
+            float v0 = stage[rr * 65 + 2 * lane], v1 = stage[rr * 65 + 2 * lane + 1];
+            if (p.gate) { v0 *= sigmoid_fast(bf16lo(gw[rr])); v1 *= sigmoid_fast(bf16hi(gw[rr])); }
+            *reinterpret_cast<float2 *>(op) = make_float2(v0, v1);
+          }
+        }
+      } else {
+        uint16_t *op = reinterpret_cast<uint16_t *>(p.out) + elem0;
 #pragma unroll
-              for (int e = 0; e < 8; ++e) o8[e] *= sigmoidf_(g8[e]);
-            }
-            if (p.out_is_f32)
-              store8<float>(reinterpret_cast<float *>(p.out) + off + v8 * 8, o8);
-            else
-              store8<uint16_t>(reinterpret_cast<uint16_t *>(p.out) + off + v8 * 8, o8);
+        for (int rr = 0; rr < 32; ++rr, op += row_stride) {
+          if (rr < nrows) {
+            float v0 = stage[rr * 65 + 2 * lane], v1 = stage[rr * 65 + 2 * lane + 1];
+            if (p.gate) { v0 *= sigmoid_fast(bf16lo(gw[rr])); v1 *= sigmoid_fast(bf16hi(gw[rr])); }
+            *reinterpret_cast<uint32_t *>(op) = pack_bf16(v0, v1);
           }
         }
       }
+      if (tid == 64) QWB_TL(18, 6);
       if (wg == 0 && row < rows_valid && p.lse) p.lse[grow] = (m_used + log2f(l_tot)) * LN2;
     }
   }
 
+  if (tid == 64) QWB_TL(19, 0);
   // ---- teardown: both CTAs meet (no signal may target a CTA that has left), then free TMEM ----
   tc_fence_before();
   __syncthreads();
