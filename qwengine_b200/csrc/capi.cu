@@ -127,6 +127,7 @@ struct AttnCall {
   bool do_rope, do_gate, no_causal;
   float *ws;
   size_t ws_floats;
+  int *cnt;  // zeroed arrival counters (one per unit) or null
   int *status;
 };
 
@@ -135,7 +136,8 @@ size_t splitkv_slot_floats(int rb) { return (size_t)rb * GROUP * PART_STRIDE; }
 
 template <int MT, int DS, int STAGES, int LOK, typename TIn, typename TOut>
 int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, cudaStream_t st) {
-  auto kern = splitkv_kernel<MT, DS, STAGES, LOK, TIn, TOut>;
+  constexpr bool FOLD = MT > 1;  // the two-row-tile variant needs the registers of an 8-warp block
+  auto kern = splitkv_kernel<MT, DS, STAGES, LOK, FOLD, TIn, TOut>;
   constexpr size_t smem = splitkv_smem_bytes<MT, DS, STAGES>();
   static bool configured[64] = {false};
   int dev = 0;
@@ -145,10 +147,11 @@ int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKV
     configured[dev] = true;
   }
   prof_mark(0, st);
-  kern<<<p.G, (SK_KS * DS + 1) * 32, smem, st>>>(mk, mv, p);
+  kern<<<p.G, (SK_KS * DS + (FOLD ? 0 : 1)) * 32, smem, st>>>(mk, mv, p);
   prof_mark(1, st);
   int rc = check_launch("splitkv_kernel");
   if (rc) return rc;
+  if (p.cnt) return QW_OK;  // units cut across CTAs were merged by their last CTA
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
   splitkv_merge_kernel<TOut><<<n_units, 256, 0, st>>>(p);
   return check_launch("splitkv_merge_kernel");
@@ -172,6 +175,7 @@ int launch_splitkv(const AttnCall &c, cudaStream_t st) {
   memset(&p, 0, sizeof(p));
   p.q = c.q; p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.partial_out = c.partial_out;
   p.pos = c.pos; p.cache_row = c.cache_row; p.mpos = c.mpos; p.ws = c.ws; p.status = c.status;
+  p.cnt = c.partial_out ? nullptr : c.cnt;
   p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.rb = splitkv_rb(c.n_new);
   p.nblk = (c.n_new + p.rb - 1) / p.rb;
@@ -198,11 +202,12 @@ int launch_splitkv(const AttnCall &c, cudaStream_t st) {
   return mt == 1 ? launch_splitkv_mt<1, 3>(c, mk, mv, p, st) : launch_splitkv_mt<2, 3>(c, mk, mv, p, st);
 }
 
-size_t splitkv_ws_floats(int n_seq, int n_new, int kv_heads) {
+long long splitkv_units(int n_seq, int n_new, int kv_heads) {
   const int rb = splitkv_rb(n_new);
-  const long long nblk = (n_new + rb - 1) / rb;
-  const long long n_units = (long long)n_seq * nblk * kv_heads;
-  return (size_t)(sm_count() + n_units) * splitkv_slot_floats(rb);
+  return (long long)n_seq * ((n_new + rb - 1) / rb) * kv_heads;
+}
+size_t splitkv_ws_floats(int n_seq, int n_new, int kv_heads) {
+  return (size_t)(sm_count() + splitkv_units(n_seq, n_new, kv_heads)) * splitkv_slot_floats(splitkv_rb(n_new));
 }
 
 bool desc_ok(const qw_mixer_desc *d) {
@@ -220,16 +225,25 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
   if (d->n_seq == 0 || d->n_new == 0) return QW_OK;
   if ((long long)d->n_seq * d->n_new > (1ll << 30)) return QW_ERR_SHAPE;
   const RopeTable tab = make_rope_table(d->theta, ROTARY_DIM);
-  if (d->flags & QW_F_APPEND) {
-    rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
-        d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
-        (d->flags & QW_F_ROPE) ? 1 : 0, tab);
-    int rc = check_launch("rope_append_kernel");
-    if (rc) return rc;
-  }
   if ((d->flags & QW_F_NO_CAUSAL) && (d->flags & QW_F_APPEND)) return QW_ERR_ARG;  // a sub-range call never owns the new rows
   const bool use_umma =
       !(d->flags & (QW_F_NO_UMMA | QW_F_NO_CAUSAL)) && !partial && prefill_umma_supported(d->n_new);
+  // Workspace: split-KV partial slots, then one arrival counter per unit.  The counters let the
+  // CTA that completes a unit last merge it inside the attention kernel; they must be zero at
+  // launch, which the rope/append kernel of the same call takes care of.
+  const long long n_units = splitkv_units(d->n_seq, d->n_new, d->kv_heads);
+  const size_t slot_floats = splitkv_ws_floats(d->n_seq, d->n_new, d->kv_heads);
+  int *cnt = nullptr;
+  if (!use_umma && !partial && (d->flags & QW_F_APPEND) && d->workspace &&
+      d->workspace_bytes >= slot_floats * sizeof(float) + (size_t)n_units * sizeof(int))
+    cnt = reinterpret_cast<int *>(reinterpret_cast<float *>(d->workspace) + slot_floats);
+  if (d->flags & QW_F_APPEND) {
+    rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
+        d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
+        (d->flags & QW_F_ROPE) ? 1 : 0, tab, cnt, cnt ? (int)n_units : 0);
+    int rc = check_launch("rope_append_kernel");
+    if (rc) return rc;
+  }
   if (use_umma) {
     PrefillCall pc;
     memset(&pc, 0, sizeof(pc));
@@ -261,7 +275,9 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
   c.q_heads = d->q_heads; c.kv_heads = d->kv_heads; c.theta = d->theta; c.scale = d->scale;
   c.do_rope = (d->flags & QW_F_ROPE) != 0; c.do_gate = (d->flags & QW_F_GATE) != 0;
   c.no_causal = (d->flags & QW_F_NO_CAUSAL) != 0;
-  c.ws = reinterpret_cast<float *>(d->workspace); c.ws_floats = d->workspace_bytes / sizeof(float);
+  c.ws = reinterpret_cast<float *>(d->workspace);
+  c.ws_floats = cnt ? slot_floats : d->workspace_bytes / sizeof(float);
+  c.cnt = cnt;
   c.status = d->status;
   if (!c.ws || (reinterpret_cast<uintptr_t>(c.ws) & 15)) return QW_ERR_WORKSPACE;
   return launch_splitkv(c, st);
@@ -478,7 +494,8 @@ int qw_attn_prefill_f32(const float *q, const qw_bf16 *kc, const qw_bf16 *vc, fl
 
 size_t qw_mixer_workspace_bytes(const qw_mixer_desc *d) {
   if (!d || d->n_seq <= 0 || d->n_new <= 0 || d->kv_heads <= 0) return 256;
-  return splitkv_ws_floats(d->n_seq, d->n_new, d->kv_heads) * sizeof(float) + 256;
+  return splitkv_ws_floats(d->n_seq, d->n_new, d->kv_heads) * sizeof(float) +
+         (size_t)splitkv_units(d->n_seq, d->n_new, d->kv_heads) * sizeof(int) + 256;
 }
 int qw_mixer_forward(const qw_mixer_desc *d, qw_stream stream) {
   return mixer_forward_impl(d, nullptr, (cudaStream_t)stream);

@@ -57,7 +57,11 @@ __global__ void __launch_bounds__(256) gate_sigmoid_kernel(T *x, const T *gate, 
 __global__ void __launch_bounds__(128) rope_append_kernel(const uint16_t *k_new, const uint16_t *v_new, uint16_t *kc,
                                                           uint16_t *vc, const int *pos, const int64_t *cache_row,
                                                           const int *mpos, int n_new, int kv_heads, int do_rope,
-                                                          const __grid_constant__ RopeTable tab) {
+                                                          const __grid_constant__ RopeTable tab, int *zero_ints,
+                                                          int n_zero) {
+  // block 0 also clears the split-KV arrival counters of the attention launch that follows
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero_ints[i] = 0;
   __shared__ double cs[ROT_PAIRS][2];
   const size_t r = blockIdx.x;  // flat row s * n_new + b
   const int s = (int)(r / n_new), b = (int)(r % n_new);

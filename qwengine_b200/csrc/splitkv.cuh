@@ -39,6 +39,7 @@ struct SplitKVParams {
   const int64_t *cache_row;  // [n_seq] or null
   const int *mpos;        // [n_seq][n_new][3] or null
   float *ws;              // (G + n_units) slots of rb*6*PART_STRIDE floats
+  int *cnt;               // per-unit arrival counters (zero at launch) or null: merge in a second kernel
   int *status;
   int n_seq, n_new, q_heads, kv_heads;
   int rb;                 // tokens per unit block
@@ -134,8 +135,77 @@ __device__ __forceinline__ uint32_t q_hi_off(int row, int d) {
   return (uint32_t)(row * 512 + ((c16 ^ (row & 7)) << 4) + ((d & 7) << 1));
 }
 
-template <int MT, int DS, int STAGES, int LOK, typename TIn, typename TOut>
-__global__ void __launch_bounds__((SK_KS * DS + 1) * 32, 1)
+// Merges the partials of one row of unit u, written by the CTAs c_first..c_last that own tiles
+// of the unit, in CTA order (fixed order => bit-stable), then normalises, gates and stores.
+// One warp per row, lane = 8 channels.  Used by the merge kernel and, when arrival counters are
+// available, by whichever CTA finishes the unit last.
+template <typename TOut>
+__device__ __forceinline__ void merge_unit_row(const SplitKVParams &p, int u, const UnitInfo &ui, int row, int c_first,
+                                               int c_last, long long total, int lane) {
+  // Partials are fetched four at a time with all their loads in flight together (a unit is
+  // usually cut into two to four pieces, so this is one L2 round trip) and folded in with a
+  // running maximum, strictly in CTA order.
+  float mg = -INFINITY, lg = 0.f;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+    float mv[4], lv[4];
+    float4 av[4], bv[4];
+    bool live[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = c0 + k;
+      live[k] = c <= c_last && (total * c / p.G != total * (c + 1) / p.G);  // CTAs without tiles wrote nothing
+      const float *src = p.ws + ((size_t)((live[k] ? c : c_first) + u) * (p.rb * GROUP) + row) * PART_STRIDE;
+      mv[k] = __ldcg(src + 256);
+      lv[k] = __ldcg(src + 257);
+      av[k] = __ldcg(reinterpret_cast<const float4 *>(src + lane * 8));
+      bv[k] = __ldcg(reinterpret_cast<const float4 *>(src + lane * 8 + 4));
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (!live[k] || !(lv[k] > 0.f)) continue;
+      const float m_new = fmaxf(mg, mv[k]);
+      const float f_old = fast_exp2(mg - m_new), f = fast_exp2(mv[k] - m_new);  // mg = -inf gives f_old = 0
+      mg = m_new;
+      lg = lg * f_old + lv[k] * f;
+      acc[0] = acc[0] * f_old + av[k].x * f; acc[1] = acc[1] * f_old + av[k].y * f;
+      acc[2] = acc[2] * f_old + av[k].z * f; acc[3] = acc[3] * f_old + av[k].w * f;
+      acc[4] = acc[4] * f_old + bv[k].x * f; acc[5] = acc[5] * f_old + bv[k].y * f;
+      acc[6] = acc[6] * f_old + bv[k].z * f; acc[7] = acc[7] * f_old + bv[k].w * f;
+    }
+  }
+  const int b = row / GROUP, hh = row % GROUP;
+  const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
+  if (p.partial_out) {
+    float *dst = p.partial_out + grow * PART_STRIDE;
+    *reinterpret_cast<float4 *>(dst + lane * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4 *>(dst + lane * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (lane == 0) { dst[256] = mg; dst[257] = lg; }
+    return;
+  }
+  const float inv = 1.f / lg;
+  if (p.do_gate) {
+    const uint4 g4 = *reinterpret_cast<const uint4 *>(p.gate + grow * HEAD_DIM + lane * 8);
+    const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc[2 * j] *= inv * sigmoidf_(bf16lo(gw[j]));
+      acc[2 * j + 1] *= inv * sigmoidf_(bf16hi(gw[j]));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv;
+  }
+  store8<TOut>(reinterpret_cast<TOut *>(p.out) + grow * HEAD_DIM + lane * 8, acc);
+  if (lane == 0 && p.lse) p.lse[grow] = (mg + log2f(lg)) * LN2;
+}
+
+// FOLD = false: a dedicated producer warp (warp NCW).  FOLD = true: lane 0 of consumer warp 0 also
+// issues the TMA loads, STAGES - 1 tiles ahead of the tile it is about to consume; the block is then
+// exactly 8 warps and every thread may use up to 255 registers (with a ninth warp the register file
+// is carved as if for twelve, which caps a thread at 168 and makes the two-row-tile variant spill).
+template <int MT, int DS, int STAGES, int LOK, bool FOLD, typename TIn, typename TOut>
+__global__ void __launch_bounds__((SK_KS * DS + (FOLD ? 0 : 1)) * 32, 1)
 splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                const __grid_constant__ SplitKVParams p) {
   constexpr int NCW = SK_KS * DS;          // consumer warps
@@ -154,6 +224,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   uint64_t *full = reinterpret_cast<uint64_t *>(lx + SK_KS * ROWS);
   uint64_t *empty = full + STAGES;
   long long *seg = reinterpret_cast<long long *>(empty + STAGES);  // [0]=total [1]=pre(u_first) [2]=u_first
+  volatile int *ticket = reinterpret_cast<volatile int *>(seg + 3);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
@@ -177,42 +248,57 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   const long long g0 = total * cta / p.G, g1 = total * (cta + 1) / p.G;
   if (g0 >= g1) return;  // uniform for the whole CTA
 
-  if (warp == NCW) {
-    // ---------------- producer: one lane streams the tiles of every segment ----------------
-    if (lane == 0) {
-      int u = (int)seg[2];
-      long long pre = seg[1];
-      uint32_t it = 0;
-      bool ok = true;
-      while (pre < g1 && u < n_units && ok) {
-        const UnitInfo ui = unit_info(p, u);
-        const int nt = (ui.len + SK_TK - 1) / SK_TK;
-        const int t0 = (int)(max(g0, pre) - pre), t1 = (int)(min(g1, pre + nt) - pre);
-        const long long row0 = p.cache_row ? p.cache_row[ui.s] : 0;
-        for (int t = t0; t < t1 && ok; ++t, ++it) {
-          const int st = it % STAGES;
-          if (it >= STAGES) {
-            if (!mbar_wait(&empty[st], ((it / STAGES) - 1) & 1)) {
-              if (p.status) *p.status = DEV_ERR_EMPTY_WAIT;
-              ok = false;
-              break;
-            }
-          }
-          uint8_t *kd = stage_base + st * SK_STAGE_BYTES, *vd = kd + SK_TILE_BYTES;
-          mbar_expect_tx(&full[st], SK_STAGE_BYTES);
-          const int r = (int)(row0 + (long long)t * SK_TK);
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            tma_load_2d(kd + c * (SK_TK * 128), &mapK, &full[st], ui.kvh * HEAD_DIM + c * 64, r);
-            tma_load_2d(vd + c * (SK_TK * 128), &mapV, &full[st], ui.kvh * HEAD_DIM + c * 64, r);
-          }
+  // ---------------- producer: one lane streams the tiles of every segment, in order -----------
+  int pu = (int)seg[2];                              // unit of the next tile to load
+  long long ppre = seg[1];                           // flat index of that unit's tile 0
+  int pt = (int)(max(g0, ppre) - ppre);              // next tile within the unit
+  uint32_t pit = 0;                                  // tiles issued so far
+  bool pok = true;
+  auto produce_one = [&]() -> bool {
+    while (ppre < g1 && pu < n_units) {
+      const UnitInfo ui = unit_info(p, pu);
+      const int nt = (ui.len + SK_TK - 1) / SK_TK;
+      const int t1 = (int)(min(g1, ppre + nt) - ppre);
+      if (pt < t1) {
+        const int st = pit % STAGES;
+        if (pit >= STAGES && !mbar_wait(&empty[st], ((pit / STAGES) - 1) & 1)) {
+          if (p.status) *p.status = DEV_ERR_EMPTY_WAIT;
+          pok = false;
+          return false;
         }
-        pre += nt;
-        ++u;
+        const long long row0 = p.cache_row ? p.cache_row[ui.s] : 0;
+        uint8_t *kd = stage_base + st * SK_STAGE_BYTES, *vd = kd + SK_TILE_BYTES;
+        mbar_expect_tx(&full[st], SK_STAGE_BYTES);
+        const int r = (int)(row0 + (long long)pt * SK_TK);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          tma_load_2d(kd + c * (SK_TK * 128), &mapK, &full[st], ui.kvh * HEAD_DIM + c * 64, r);
+          tma_load_2d(vd + c * (SK_TK * 128), &mapV, &full[st], ui.kvh * HEAD_DIM + c * 64, r);
+        }
+        ++pt;
+        ++pit;
+        return true;
       }
+      ppre += nt;
+      ++pu;
+      pt = 0;
     }
+    return false;
+  };
+  if (!FOLD && warp == NCW) {
+    if (lane == 0)
+      while (produce_one()) { }
     return;
   }
+  // folded producer: keep the ring full up to STAGES - 1 tiles past the one about to be consumed
+  auto produce_ahead = [&](uint32_t consume_it) {
+    if (FOLD && warp == 0) {
+      if (lane == 0)
+        while (pok && pit < consume_it + STAGES && produce_one()) { }
+      __syncwarp();
+    }
+  };
+  produce_ahead(0);
 
   // ---------------------------- consumers ---------------------------------------------------
   const int ks = warp % SK_KS, ds = warp / SK_KS;
@@ -321,6 +407,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
 
     for (int t = t0; t < t1; ++t, ++it) {
       const int st = it % STAGES;
+      produce_ahead(it);
       if (ok) {
         // every lane polls; the verdict is made warp-uniform before any warp-wide operation
         const bool got = mbar_wait(&full[st], (it / STAGES) & 1);
@@ -540,6 +627,21 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         if (c8 == 0) { dst[256] = mg; dst[257] = lg; }
       }
     }
+    // ---- with arrival counters: the CTA that completes a unit last merges it right here ----
+    if (!whole && p.cnt) {
+      __threadfence();  // this thread's partial stores are visible device-wide before the ticket
+      consumer_sync(NCT);
+      if (tid == 0) *ticket = atomicAdd(&p.cnt[u], 1);
+      consumer_sync(NCT);
+      const int c_first = cta_of_tile(pre, total, p.G), c_last = cta_of_tile(pre + nt_unit - 1, total, p.G);
+      int nparts = 0;
+      for (int c = c_first; c <= c_last; ++c) nparts += (total * c / p.G != total * (c + 1) / p.G) ? 1 : 0;
+      if (*ticket == nparts - 1) {
+        __threadfence();
+        for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane);
+        if (tid == 0) p.cnt[u] = 0;  // leave the counter clean for a caller that does not reset it
+      }
+    }
     pre += nt_unit;
     ++u;
   }
@@ -565,53 +667,7 @@ __global__ void __launch_bounds__(256) splitkv_merge_kernel(const __grid_constan
   const int c_first = cta_of_tile(pre, total, p.G), c_last = cta_of_tile(pre + nt - 1, total, p.G);
   if (c_first == c_last) return;  // the main kernel already wrote this unit
   const int R = ui.ntok * GROUP;
-  for (int row = warp; row < R; row += 8) {
-    float mg = -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (total * c / p.G == total * (c + 1) / p.G) continue;  // this CTA owned no tile and wrote nothing
-      const float *src = p.ws + ((size_t)(c + u) * (p.rb * GROUP) + row) * PART_STRIDE;
-      if (src[257] > 0.f) mg = fmaxf(mg, src[256]);
-    }
-    const float m_use = (mg == -INFINITY) ? 0.f : mg;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    float lg = 0.f;
-    for (int c = c_first; c <= c_last; ++c) {
-      if (total * c / p.G == total * (c + 1) / p.G) continue;
-      const float *src = p.ws + ((size_t)(c + u) * (p.rb * GROUP) + row) * PART_STRIDE;
-      const float l = src[257];
-      if (!(l > 0.f)) continue;
-      const float f = fast_exp2(src[256] - m_use);
-      lg += l * f;
-      const float4 a = *reinterpret_cast<const float4 *>(src + lane * 8);
-      const float4 b = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
-      acc[0] += a.x * f; acc[1] += a.y * f; acc[2] += a.z * f; acc[3] += a.w * f;
-      acc[4] += b.x * f; acc[5] += b.y * f; acc[6] += b.z * f; acc[7] += b.w * f;
-    }
-    const int b = row / GROUP, hh = row % GROUP;
-    const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
-    if (p.partial_out) {
-      float *dst = p.partial_out + grow * PART_STRIDE;
-      *reinterpret_cast<float4 *>(dst + lane * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      *reinterpret_cast<float4 *>(dst + lane * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
-      if (lane == 0) { dst[256] = mg; dst[257] = lg; }
-      continue;
-    }
-    const float inv = 1.f / lg;
-    if (p.do_gate) {
-      const uint4 g4 = *reinterpret_cast<const uint4 *>(p.gate + grow * HEAD_DIM + lane * 8);
-      const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        acc[2 * j] *= inv * sigmoidf_(bf16lo(gw[j]));
-        acc[2 * j + 1] *= inv * sigmoidf_(bf16hi(gw[j]));
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] *= inv;
-    }
-    store8<TOut>(reinterpret_cast<TOut *>(p.out) + grow * HEAD_DIM + lane * 8, acc);
-    if (lane == 0 && p.lse) p.lse[grow] = (mg + log2f(lg)) * LN2;
-  }
+  for (int row = warp; row < R; row += 8) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane);
 }
 
 // Merge n_parts partial sets [n_parts][n][PART_STRIDE] (n = rows * q_heads) in index order, then
