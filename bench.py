@@ -218,7 +218,8 @@ def measure(name, args, rank, world, flags_extra=0, with_e2e=True):
         torch.distributed.all_reduce(sums, op=torch.distributed.ReduceOp.SUM)
     total_ms, e2e_ms, k_ms = [float(x) for x in stats.cpu()]
     kv_all, flops_all = [float(x) for x in sums.cpu()]
-    return {"w": w, "steps": steps, "warmup": warm, "ms_per_step": total_ms / steps, "e2e_ms_per_step": e2e_ms / steps,
+    return {"w": w, "steps": steps, "warmup": warm, "ms_per_step": total_ms / steps,
+            "e2e_ms_per_step": (e2e_ms / steps) if with_e2e else None,
             "kernel_ms": k_ms, "kv_bytes_all": kv_all, "flops_all": flops_all, "launches": launches * steps,
             "h2d": h2d, "d2h": d2h}
 
@@ -266,10 +267,10 @@ def tensor_line(name, r, world, peaks, mode):
                                 % (3 * w["q"].numel() * 2 / 1e6)},
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": tc_peak, "unit": "TFLOP/s",
                      "frac": round(achieved / tc_peak, 4), "traffic": None, "peak_kind": kind,
-                     "kernel": "prefill_umma_kernel", "kernel_ms": round(r["kernel_ms"], 5),
+                     "kernel": "prefill_umma_pair_kernel", "kernel_ms": round(r["kernel_ms"], 5),
                      "flops_counted": "4*256*24 per unmasked (query,key) pair; the bf16 lo pass of P is not counted"},
-        "e2e": {"value": round(r["flops_all"] / (r["e2e_ms_per_step"] * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
-                "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
+        "e2e": {"value": round(r["flops_all"] / (r["e2e_ms_per_step"] * 1e-3) / 1e12, 1) if r["e2e_ms_per_step"] else None,
+                "unit": "TFLOP/s", "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
         "gpu_launches": r["launches"],
     }
 
