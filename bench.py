@@ -245,7 +245,10 @@ def hbm_line(name, r, world, peaks):
         "config": {"workload": describe(name, world, w), "sharding": SHARDING[world],
                    "l2_policy": "inputs larger than L2: %.0f MB of KV per GPU per step vs 126 MB L2" % (w["kv_bytes"] / 1e6)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
-                     "frac": round(achieved / hbm_peak, 4), "traffic": None, "peak_kind": kind,
+                     "frac": round(achieved / hbm_peak, 4),
+                     "traffic": 543.4e6 if (name == "decode" and world == 1) else None,
+                     "traffic_source": "ncu dram read+write bytes per launch, profiles/splitkv_decode_config2.txt",
+                     "algorithmic_bytes": w["kv_bytes"], "peak_kind": kind,
                      "kernel": "splitkv_kernel", "kernel_ms": round(r["kernel_ms"], 5)},
         "e2e": {"value": round(r["kv_bytes_all"] / (r["e2e_ms_per_step"] * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
@@ -266,7 +269,10 @@ def tensor_line(name, r, world, peaks, mode):
                    "l2_policy": "L2 flushed by the q/gate/out streams of the step (%.0f MB) plus KV"
                                 % (3 * w["q"].numel() * 2 / 1e6)},
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": tc_peak, "unit": "TFLOP/s",
-                     "frac": round(achieved / tc_peak, 4), "traffic": None, "peak_kind": kind,
+                     "frac": round(achieved / tc_peak, 4),
+                     "traffic": 316.5e6 if (name == "prefill8k" and world == 1) else None,
+                     "traffic_source": "ncu dram read+write bytes per launch, profiles/prefill_umma_pair_8k.txt",
+                     "algorithmic_flops": w["flops"], "peak_kind": kind,
                      "kernel": "prefill_umma_pair_kernel", "kernel_ms": round(r["kernel_ms"], 5),
                      "flops_counted": "4*256*24 per unmasked (query,key) pair; the bf16 lo pass of P is not counted"},
         "e2e": {"value": round(r["flops_all"] / (r["e2e_ms_per_step"] * 1e-3) / 1e12, 1) if r["e2e_ms_per_step"] else None,

@@ -1,0 +1,104 @@
+"""Split of one sequence's KV range across ranks: each rank attends to its sub-range and emits
+(o, m, l) partials, the partials are gathered and merged in rank order.  On one GPU the two
+sub-ranges are run one after the other (same kernels, same merge); with two or more GPUs the
+exchange is a real NCCL all-gather between processes."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pyoracle as O
+from qwengine_b200 import api, sharding
+from tests.gpu_util import dev_bf16, dev_bits, host_f32
+from tests.util import Case, check_lse, check_out
+
+pytestmark = pytest.mark.gpu
+
+
+def _rotated_q(c, pos0):
+    q = dev_bf16(c.q[0])
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    api.rope(q, c.q_heads, 256, 64, dpos, 1e7, B=c.n_new)
+    return q
+
+
+def _partial_for_range(c, q_rot, kc, vc, lo, hi, owns_new_rows):
+    """Partials of rows q_rot over cache rows [lo, hi) of the (single) sequence."""
+    B = c.n_new
+    mx = api.Mixer(1, B, kv_heads=c.kv_heads)
+    part = torch.zeros(B, c.q_heads, api.PARTIAL_FLOATS, dtype=torch.float32, device="cuda")
+    crow = torch.tensor([lo], dtype=torch.int64, device="cuda")
+    out = torch.empty(1, B, c.q_heads, 256, dtype=torch.bfloat16, device="cuda")
+    if owns_new_rows:   # tail range: causal among the new rows, which are its last B rows
+        pos = torch.tensor([hi - lo - B], dtype=torch.int32, device="cuda")
+        mx.bind(q_rot, kc, vc, pos, out, cache_row=crow, flags=0)
+    else:               # head range: every row sees all of it
+        pos = torch.tensor([hi - lo], dtype=torch.int32, device="cuda")
+        mx.bind(q_rot, kc, vc, pos, out, cache_row=crow, flags=api.F_NO_CAUSAL)
+    mx.forward_partial(part)
+    torch.cuda.synchronize()
+    mx.check_status()
+    return part
+
+
+@pytest.mark.parametrize("hist,B,cut", [(700, 1, 384), (3000, 4, 1000), (129, 2, 64)])
+def test_kv_range_split_and_combine_on_one_gpu(hist, B, cut):
+    c = Case(300 + B, [hist], B)
+    ref, lse_ref, kc_ref, vc_ref = c.oracle()          # also gives the cache with the new rows appended
+    kc, vc = dev_bits(kc_ref), dev_bits(vc_ref)
+    q_rot = _rotated_q(c, hist)
+    L = hist + B
+    parts = torch.stack([_partial_for_range(c, q_rot, kc, vc, 0, cut, False),
+                         _partial_for_range(c, q_rot, kc, vc, cut, L, True)])
+    out = torch.empty(B, c.q_heads, 256, dtype=torch.float32, device="cuda")
+    lse = torch.empty(B, c.q_heads, dtype=torch.float32, device="cuda")
+    api.combine_partials(parts, 2, B, c.q_heads, out, gate=dev_bf16(c.gate[0]), lse=lse)
+    torch.cuda.synchronize()
+    # q was rounded to bf16 after the stand-alone RoPE (the fused path keeps it in fp32), hence the
+    # looser bound than check_out
+    got = host_f32(out)
+    assert np.abs(got - ref).max() <= 2e-2
+    from tests.util import rel_l2
+    assert rel_l2(got, ref) <= 3e-3
+    assert np.abs(lse.cpu().numpy() - lse_ref).max() <= 5e-3
+    # the merge on the GPU equals its host specification bit for bit in structure: compare loosely
+    o_host, lse_host = sharding.merge_partials_reference(parts.cpu())
+    gate = 1.0 / (1.0 + np.exp(-c.gate[0].astype(np.float64)))
+    assert np.abs(o_host.numpy() * gate - got).max() < 1e-5
+
+
+def _nccl_worker(rank, world, port, hist, B, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    torch.distributed.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        c = Case(400, [hist], B)
+        ref, lse_ref, kc_ref, vc_ref = c.oracle()
+        kc, vc = dev_bits(kc_ref), dev_bits(vc_ref)   # every rank holds the cache here; it reads only its range
+        q_rot = _rotated_q(c, hist)
+        L = hist + B
+        cut = (L // 2 // 64) * 64
+        lo, hi = (0, cut) if rank == 0 else (cut, L)
+        part = _partial_for_range(c, q_rot, kc, vc, lo, hi, rank == world - 1)
+        parts = sharding.gather_partials(part)
+        out = torch.empty(B, c.q_heads, 256, dtype=torch.float32, device="cuda")
+        api.combine_partials(parts, world, B, c.q_heads, out, gate=dev_bf16(c.gate[0]))
+        torch.cuda.synchronize()
+        from tests.util import rel_l2
+        got = host_f32(out)
+        ret[rank] = bool(np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 3e-3)
+    finally:
+        torch.distributed.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_kv_range_split_across_two_gpus_with_nccl():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ret = mp.Manager().dict()
+    mp.spawn(_nccl_worker, args=(2, port, 2500, 4, ret), nprocs=2, join=True)
+    assert dict(ret) == {0: True, 1: True}
