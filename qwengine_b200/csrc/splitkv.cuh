@@ -214,6 +214,9 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   constexpr int DW = HEAD_DIM / DS;        // output channels per warp
   constexpr int NT_O = DW / 8;             // 8-wide output n-tiles per warp
   constexpr int QREGION = ROWS * 1024;     // q_hi + q_lo (bf16) or combine buffer (fp32)
+  // With one 16-row tile and the 8-warp block there are registers to spare: the Q fragments of all
+  // k-steps then live in registers for the whole segment instead of being re-read per KV tile.
+  constexpr bool QREG = FOLD && MT == 1 && LOK <= 4;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -383,6 +386,14 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       }
     }
     consumer_sync(NCT);
+    uint32_t qf[QREG ? 16 : 1][4], qlf[QREG && LOK > 0 ? LOK : 1][4];
+    if (QREG) {
+#pragma unroll
+      for (int kk = 0; kk < 16; ++kk) ldsm_x4(qlane[0][kk & 3] + (kk >> 2) * 128, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+#pragma unroll
+      for (int kk = 0; kk < LOK; ++kk)
+        ldsm_x4(qlane[0][kk & 3] + (kk >> 2) * 128 + ROWS * 512, qlf[kk][0], qlf[kk][1], qlf[kk][2], qlf[kk][3]);
+    }
 
     // ---- per-row state ----
     float o[MT][NT_O][4];
@@ -440,7 +451,8 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             uint32_t a0, a1, a2, a3;
-            ldsm_x4(qlane[mt][kk & 3] + (kk >> 2) * 128, a0, a1, a2, a3);
+            if (QREG) { a0 = qf[kk][0]; a1 = qf[kk][1]; a2 = qf[kk][2]; a3 = qf[kk][3]; }
+            else ldsm_x4(qlane[mt][kk & 3] + (kk >> 2) * 128, a0, a1, a2, a3);
             if (kk & 1) {
               mma_bf16_16816(s2[mt][0], a0, a1, a2, a3, b0, b1);
               mma_bf16_16816(s2[mt][1], a0, a1, a2, a3, b2, b3);
@@ -449,7 +461,8 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
               mma_bf16_16816(s[mt][1], a0, a1, a2, a3, b2, b3);
             }
             if (kk < LOK) {  // the bf16 "lo" part of Q against the same K fragment
-              ldsm_x4(qlane[mt][kk & 3] + (kk >> 2) * 128 + ROWS * 512, a0, a1, a2, a3);
+              if (QREG) { a0 = qlf[kk][0]; a1 = qlf[kk][1]; a2 = qlf[kk][2]; a3 = qlf[kk][3]; }
+              else ldsm_x4(qlane[mt][kk & 3] + (kk >> 2) * 128 + ROWS * 512, a0, a1, a2, a3);
               if (kk & 1) {
                 mma_bf16_16816(s[mt][0], a0, a1, a2, a3, b0, b1);
                 mma_bf16_16816(s[mt][1], a0, a1, a2, a3, b2, b3);
