@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libqwengine_attn.so")
-SOURCES = ["capi.cu", "prefill_umma.cu", "prefill_umma2.cu"]
+SOURCES = ["capi.cu", "prefill_umma.cu", "prefill_umma2.cu", "splitkv_umma.cu"]
 
 
 def nvcc_cmd(verbose=False):

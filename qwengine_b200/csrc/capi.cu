@@ -4,6 +4,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -11,6 +12,7 @@
 #include "elementwise.cuh"
 #include "prefill_umma.cuh"
 #include "splitkv.cuh"
+#include "splitkv_umma.cuh"
 
 using namespace qwb;
 
@@ -213,6 +215,70 @@ size_t splitkv_ws_floats(int n_seq, int n_new, int kv_heads) {
   return (size_t)(sm_count() + splitkv_units(n_seq, n_new, kv_heads)) * splitkv_slot_floats(splitkv_rb(n_new));
 }
 
+// Workspace of the fused mixer: [arrival counters][partial slots].  Sized for whichever split-KV
+// kernel needs more (the mma.sync kernel cuts new tokens into blocks of 5, the tcgen05 one of 21).
+long long umma_units(int n_seq, int n_new, int kv_heads) {
+  const int rb = splitkv_umma_rb(n_new);
+  return (long long)n_seq * ((n_new + rb - 1) / rb) * kv_heads;
+}
+size_t mixer_cnt_bytes(int n_seq, int n_new, int kv_heads) {
+  long long n = splitkv_units(n_seq, n_new, kv_heads);
+  if (splitkv_umma_usable(n_new) && umma_units(n_seq, n_new, kv_heads) > n) n = umma_units(n_seq, n_new, kv_heads);
+  return ((size_t)n * sizeof(int) + 255) & ~(size_t)255;
+}
+size_t mixer_slot_floats(int n_seq, int n_new, int kv_heads) {
+  size_t f = splitkv_ws_floats(n_seq, n_new, kv_heads);
+  if (splitkv_umma_usable(n_new)) {
+    const size_t g = (size_t)(sm_count() + umma_units(n_seq, n_new, kv_heads)) * splitkv_slot_floats(splitkv_umma_rb(n_new));
+    if (g > f) f = g;
+  }
+  return f;
+}
+// Which split-KV kernel serves chunks of n_new < 64 tokens in the fused path: the tcgen05 one for
+// two or more new tokens (environment QWB_DECODE_KERNEL=umma / mma overrides, for experiments).
+bool prefer_umma_decode(int n_new) {
+  static int mode = -1;
+  if (mode < 0) {
+    const char *e = getenv("QWB_DECODE_KERNEL");
+    mode = !e ? 0 : (e[0] == 'u' ? 1 : (e[0] == 'm' ? 2 : 0));
+  }
+  if (mode == 1) return true;
+  if (mode == 2) return false;
+  return n_new >= 2;
+}
+
+int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
+  SplitKVParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = c.q; p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.partial_out = nullptr;
+  p.pos = c.pos; p.cache_row = c.cache_row; p.mpos = c.mpos; p.ws = c.ws; p.status = c.status; p.cnt = c.cnt;
+  p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
+  p.rb = splitkv_umma_rb(c.n_new);
+  p.nblk = (c.n_new + p.rb - 1) / p.rb;
+  const long long n_units = (long long)c.n_seq * p.nblk * c.kv_heads;
+  if (n_units > (1 << 24)) return QW_ERR_SHAPE;
+  const long long max_slots = (long long)(c.ws_floats / splitkv_slot_floats(p.rb));
+  long long G = sm_count();
+  if (max_slots - n_units < G) G = max_slots - n_units;
+  if (G < 1) return QW_ERR_WORKSPACE;
+  p.G = (int)G;
+  p.q_lo_dims = c.do_rope ? ROTARY_DIM : 0;
+  p.scale_log2 = c.scale * LOG2E;
+  p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate; p.no_causal = c.no_causal;
+  p.rope = make_rope_table(c.theta, ROTARY_DIM);
+  CUtensorMap mk, mv;
+  int rc = make_rowmajor_map(&mk, c.kc, c.cache_rows, c.kv_heads * HEAD_DIM, 128);
+  if (rc) return rc;
+  rc = make_rowmajor_map(&mv, c.vc, c.cache_rows, c.kv_heads * HEAD_DIM, 32);
+  if (rc) return rc;
+  prof_mark(0, st);
+  rc = launch_splitkv_umma(mk, mv, p, c.out_is_f32, st);
+  prof_mark(1, st);
+  ++g_launches;
+  if (rc == QW_ERR_CUDA) return cuda_fail(cudaGetLastError(), "splitkv_umma_kernel");
+  return rc;
+}
+
 bool desc_ok(const qw_mixer_desc *d) {
   if (!d || d->n_seq < 0 || d->n_new < 0) return false;
   if (!d->q || !d->out || !d->kc || !d->vc || !d->pos || d->cache_rows <= 0) return false;
@@ -231,15 +297,14 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
   if ((d->flags & QW_F_NO_CAUSAL) && (d->flags & QW_F_APPEND)) return QW_ERR_ARG;  // a sub-range call never owns the new rows
   const bool use_umma =
       !(d->flags & (QW_F_NO_UMMA | QW_F_NO_CAUSAL)) && !partial && prefill_umma_supported(d->n_new);
-  // Workspace: split-KV partial slots, then one arrival counter per unit.  The counters let the
-  // CTA that completes a unit last merge it inside the attention kernel; they must be zero at
+  // Workspace: arrival counters (one per unit), then the split-KV partial slots.  The counters let
+  // the CTA that completes a unit last merge it inside the attention kernel; they must be zero at
   // launch, which the rope/append kernel of the same call takes care of.
-  const long long n_units = splitkv_units(d->n_seq, d->n_new, d->kv_heads);
-  const size_t slot_floats = splitkv_ws_floats(d->n_seq, d->n_new, d->kv_heads);
+  const size_t cnt_bytes = mixer_cnt_bytes(d->n_seq, d->n_new, d->kv_heads);
   int *cnt = nullptr;
-  if (!use_umma && !partial && (d->flags & QW_F_APPEND) && d->workspace &&
-      d->workspace_bytes >= slot_floats * sizeof(float) + (size_t)n_units * sizeof(int))
-    cnt = reinterpret_cast<int *>(reinterpret_cast<float *>(d->workspace) + slot_floats);
+  if (!use_umma && !partial && (d->flags & QW_F_APPEND) && d->workspace && d->workspace_bytes > cnt_bytes)
+    cnt = reinterpret_cast<int *>(d->workspace);
+  const long long n_units = (long long)(cnt_bytes / sizeof(int));
   if (d->flags & QW_F_APPEND) {
     rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
         d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
@@ -278,11 +343,14 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
   c.q_heads = d->q_heads; c.kv_heads = d->kv_heads; c.theta = d->theta; c.scale = d->scale;
   c.do_rope = (d->flags & QW_F_ROPE) != 0; c.do_gate = (d->flags & QW_F_GATE) != 0;
   c.no_causal = (d->flags & QW_F_NO_CAUSAL) != 0;
-  c.ws = reinterpret_cast<float *>(d->workspace);
-  c.ws_floats = cnt ? slot_floats : d->workspace_bytes / sizeof(float);
+  if (!d->workspace || (reinterpret_cast<uintptr_t>(d->workspace) & 15) || d->workspace_bytes <= cnt_bytes)
+    return QW_ERR_WORKSPACE;
+  c.ws = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(d->workspace) + cnt_bytes);
+  c.ws_floats = (d->workspace_bytes - cnt_bytes) / sizeof(float);
   c.cnt = cnt;
   c.status = d->status;
-  if (!c.ws || (reinterpret_cast<uintptr_t>(c.ws) & 15)) return QW_ERR_WORKSPACE;
+  if (cnt && !(d->flags & QW_F_NO_UMMA) && splitkv_umma_usable(d->n_new) && prefer_umma_decode(d->n_new))
+    return launch_splitkv_umma_call(c, st);
   return launch_splitkv(c, st);
 }
 
@@ -497,8 +565,8 @@ int qw_attn_prefill_f32(const float *q, const qw_bf16 *kc, const qw_bf16 *vc, fl
 
 size_t qw_mixer_workspace_bytes(const qw_mixer_desc *d) {
   if (!d || d->n_seq <= 0 || d->n_new <= 0 || d->kv_heads <= 0) return 256;
-  return splitkv_ws_floats(d->n_seq, d->n_new, d->kv_heads) * sizeof(float) +
-         (size_t)splitkv_units(d->n_seq, d->n_new, d->kv_heads) * sizeof(int) + 256;
+  return mixer_cnt_bytes(d->n_seq, d->n_new, d->kv_heads) +
+         mixer_slot_floats(d->n_seq, d->n_new, d->kv_heads) * sizeof(float) + 256;
 }
 int qw_mixer_forward(const qw_mixer_desc *d, qw_stream stream) {
   return mixer_forward_impl(d, nullptr, (cudaStream_t)stream);

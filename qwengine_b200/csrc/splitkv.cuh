@@ -71,20 +71,23 @@ __device__ __forceinline__ UnitInfo unit_info(const SplitKVParams &p, int u) {
   ui.len = p.no_causal ? ui.pos : ui.pos + ui.tok0 + ui.ntok;
   return ui;
 }
+template <int TK = SK_TK>
 __device__ __forceinline__ int unit_tiles(const SplitKVParams &p, int u) {
   const UnitInfo ui = unit_info(p, u);
-  return (ui.len + SK_TK - 1) / SK_TK;
+  return (ui.len + TK - 1) / TK;
 }
 
 // Warp-cooperative: total number of tiles over all units.
+template <int TK = SK_TK>
 __device__ __forceinline__ long long warp_total_tiles(const SplitKVParams &p, int n_units, int lane) {
   long long t = 0;
-  for (int u = lane; u < n_units; u += 32) t += unit_tiles(p, u);
+  for (int u = lane; u < n_units; u += 32) t += unit_tiles<TK>(p, u);
 #pragma unroll
   for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
   return t;
 }
 // Warp-cooperative: the unit containing flat tile g and the flat index of that unit's tile 0.
+template <int TK = SK_TK>
 __device__ __forceinline__ void warp_find_unit(const SplitKVParams &p, int n_units, int lane, long long g,
                                                int &u_out, long long &pre_out) {
   long long carry = 0;
@@ -92,7 +95,7 @@ __device__ __forceinline__ void warp_find_unit(const SplitKVParams &p, int n_uni
   pre_out = 0;
   for (int base = 0; base < n_units; base += 32) {
     const int u = base + lane;
-    const long long mine = u < n_units ? unit_tiles(p, u) : 0;
+    const long long mine = u < n_units ? unit_tiles<TK>(p, u) : 0;
     long long inc = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -112,9 +115,10 @@ __device__ __forceinline__ void warp_find_unit(const SplitKVParams &p, int n_uni
   }
 }
 // Warp-cooperative: flat index of tile 0 of unit u.
+template <int TK = SK_TK>
 __device__ __forceinline__ long long warp_unit_prefix(const SplitKVParams &p, int u_target, int lane) {
   long long t = 0;
-  for (int u = lane; u < u_target; u += 32) t += unit_tiles(p, u);
+  for (int u = lane; u < u_target; u += 32) t += unit_tiles<TK>(p, u);
 #pragma unroll
   for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
   return t;

@@ -1,0 +1,515 @@
+// Split-KV attention for decode / speculative verify / short chunks on the tcgen05 tensor cores.
+//
+// Same work model as splitkv.cuh (units = (sequence, block of new tokens, KV head); all KV tiles of
+// all units in one flat list cut evenly over a persistent grid; partials merged in CTA order by the
+// CTA that completes a unit last), but the tile arithmetic runs on UMMA instead of mma.sync:
+// a unit's query rows (token b, head hh) -> row 6 b + hh fill the first R <= 126 rows of a 128-row
+// Q tile, S = Q K^T is a 128 x 128 x 256 tcgen05.mma per 128-key tile and O += P V a 128 x 256 x 128
+// one with P (bf16 hi + lo) in tensor memory.  The rows beyond R are padding: the tensor pipe has
+// the slack (3.3k cycles of MMA per 128 KB tile against ~5.4k cycles of HBM time per SM), and in
+// exchange the per-tile instruction stream of the CUDA cores shrinks to the softmax of R rows, so
+// the kernel stays HBM-bound for 24-row verify batches where the mma.sync kernel is issue-bound.
+//
+// Layout and roles follow prefill_umma.cu: TMEM O | S0 | S1 (P over S), K/V through a ring of
+// eight 16 KB TMA slots released by tcgen05.commit, warp 0 = producer, warp 1 = MMA issuer and
+// TMEM owner, warps 2..17 = four softmax warpgroups (thread = row, warpgroup = 32-key column group
+// and 64-channel output group).  Differences: Q is staged by the softmax threads themselves (plain
+// loads, RoPE in double, bf16 hi + lo, written in the swizzled UMMA layout); each row has its own
+// causal limit; a CTA walks several segments (unit, tile range), so every barrier phase is tracked
+// with CTA-cumulative counters; a segment ends in a final store or in a partial + arrival ticket.
+#include <cstring>
+
+#include "splitkv.cuh"
+#include "splitkv_umma.cuh"
+#include "umma_common.cuh"
+
+namespace qwb {
+
+namespace {
+
+constexpr int DU_BN = 128;                 // keys per tile
+constexpr int DU_SLOT = 16384;
+constexpr int DU_NSLOT = 8;
+constexpr int DU_QBYTES = 5 * DU_SLOT;     // four 64-channel sub-tiles of 128 rows + the rotary "lo" sub-tile
+constexpr int DU_NWG = 4;
+constexpr int DU_SM_THREADS = DU_NWG * 128;
+constexpr int DU_THREADS = 64 + DU_SM_THREADS;
+
+struct DecCtl {
+  uint64_t q_ready, o_free, s_full[2], p_full[2], o_done[2];
+  uint64_t slot_full[DU_NSLOT], slot_empty[DU_NSLOT];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  volatile int ticket;
+  long long part[3];             // total tiles, flat index of the first unit's tile 0, first unit
+  float mxbuf[2][DU_NWG][128];
+  float lbuf[DU_NWG][128];
+};
+
+// Byte offset of element (row, d) of the 128-row Q tile: 64-channel sub-tiles of 128-byte rows,
+// 16-byte column XOR (row & 7) -- the K-major 128-byte-swizzle operand layout.
+__device__ __forceinline__ uint32_t q_tile_off(int row, int d) {
+  return (uint32_t)((d >> 6) * DU_SLOT + row * 128 + ((((d >> 3) & 7) ^ (row & 7)) << 4) + ((d & 7) << 1));
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(DU_THREADS, 1)
+splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                    const __grid_constant__ SplitKVParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t *q_smem = smem;
+  uint8_t *ring = smem + DU_QBYTES;
+  DecCtl *ctl = reinterpret_cast<DecCtl *>(ring + DU_NSLOT * DU_SLOT);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_units = p.n_seq * p.nblk * p.kv_heads;
+  const int cta = blockIdx.x;
+
+  if (tid == 0) {
+    mbar_init(&ctl->q_ready, DU_SM_THREADS);
+    mbar_init(&ctl->o_free, DU_SM_THREADS);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ctl->s_full[i], 1);
+      mbar_init(&ctl->p_full[i], DU_SM_THREADS);
+      mbar_init(&ctl->o_done[i], 1);
+    }
+    for (int i = 0; i < DU_NSLOT; ++i) { mbar_init(&ctl->slot_full[i], 1); mbar_init(&ctl->slot_empty[i], 1); }
+    ctl->abort_flag = (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) ? 1 : 0;
+    fence_barrier_init();
+    prefetch_tensormap(&mapK);
+    prefetch_tensormap(&mapV);
+  }
+  if (warp == 2) {
+    const long long total = warp_total_tiles<DU_BN>(p, n_units, lane);
+    const long long g0 = total * cta / p.G;
+    int u0; long long pre0;
+    warp_find_unit<DU_BN>(p, n_units, lane, g0, u0, pre0);
+    if (lane == 0) { ctl->part[0] = total; ctl->part[1] = pre0; ctl->part[2] = u0; }
+  }
+  __syncthreads();
+  const long long total = ctl->part[0];
+  const long long g0 = total * cta / p.G, g1 = total * (cta + 1) / p.G;
+  if (g0 >= g1 || ctl->abort_flag) return;  // uniform: nothing to do, or the launch already failed
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  volatile int *abort_flag = &ctl->abort_flag;
+  auto fail = [&](int code) {
+    if (!*abort_flag && p.status) *p.status = code;
+    *abort_flag = 1;
+  };
+
+  if (warp == 0) {
+    // =============================== TMA producer ===========================================
+    // Per segment the slot stream is  K_t0 | K_t0+1 V_t0 | ... | V_t1-1 ; segments follow each
+    // other without a gap.  A K slot is one 64-channel sub-tile of 128 keys, a V slot 32 keys x 256.
+    if (lane == 0) {
+      int u = (int)ctl->part[2];
+      long long pre = ctl->part[1];
+      uint32_t it = 0;
+      bool ok = true;
+      auto slot_ready = [&]() -> bool {
+        const int sl = it % DU_NSLOT;
+        if (it >= DU_NSLOT && !wait_or_abort(&ctl->slot_empty[sl], ((it / DU_NSLOT) - 1) & 1, abort_flag)) {
+          fail(DEV_ERR_EMPTY_WAIT);
+          ok = false;
+          return false;
+        }
+        mbar_expect_tx(&ctl->slot_full[sl], DU_SLOT);
+        return true;
+      };
+      while (pre < g1 && u < n_units && ok) {
+        const UnitInfo ui = unit_info(p, u);
+        const int nt = (ui.len + DU_BN - 1) / DU_BN;
+        const int t0 = (int)(max(g0, pre) - pre), t1 = (int)(min(g1, pre + nt) - pre);
+        const long long row0 = p.cache_row ? p.cache_row[ui.s] : 0;
+        for (int j = t0; j <= t1 && ok; ++j) {
+          if (j < t1) {
+            for (int c = 0; c < 4 && ok; ++c) {
+              if (!slot_ready()) break;
+              const int sl = it % DU_NSLOT;
+              tma_load_2d(ring + sl * DU_SLOT, &mapK, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
+                          (int)(row0 + (long long)j * DU_BN));
+              ++it;
+            }
+          }
+          if (j > t0 && ok) {
+            for (int g = 0; g < 4 && ok; ++g) {
+              if (!slot_ready()) break;
+              const int sl = it % DU_NSLOT;
+#pragma unroll
+              for (int c = 0; c < 4; ++c)  // 32 keys x 64 channels each, channel atoms 4 KB apart
+                tma_load_2d(ring + sl * DU_SLOT + c * 4096, &mapV, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
+                            (int)(row0 + (long long)(j - 1) * DU_BN + g * 32));
+              ++it;
+            }
+          }
+        }
+        pre += nt;
+        ++u;
+      }
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer ==============================================
+    // The whole warp walks the tile sequence (so that it can clear ragged V rows together); lane 0
+    // issues.  J counts tiles over all segments of this CTA: S / P buffer J & 1, barrier phase J >> 1.
+    const uint32_t idesc_qk = make_idesc(128, 128, 1, 1, 0, 0);
+    const uint32_t idesc_pv = make_idesc(128, 256, 1, 1, 0, 1);
+    const uint64_t qdesc0 = smem_desc(smem_u32(q_smem), 16, 1024);
+    const uint64_t kdesc0 = smem_desc(smem_u32(ring), 16, 1024);
+    const uint64_t vdesc0 = smem_desc(smem_u32(ring), 4096, 1024);
+    int u = (int)ctl->part[2];
+    long long pre = ctl->part[1];
+    uint32_t it = 0;
+    int J = 0, seg = 0;
+    bool ok = true;
+    auto wait_all = [&](uint64_t *bar, uint32_t parity, int code) {
+      bool got = wait_or_abort(bar, parity, abort_flag);
+      got = __all_sync(0xffffffffu, got);
+      if (!got) {
+        if (lane == 0) fail(code);
+        ok = false;
+      }
+      return got;
+    };
+    while (pre < g1 && u < n_units && ok) {
+      const UnitInfo ui = unit_info(p, u);
+      const int nt = (ui.len + DU_BN - 1) / DU_BN;
+      const int t0 = (int)(max(g0, pre) - pre), t1 = (int)(min(g1, pre + nt) - pre);
+      if (!wait_all(&ctl->q_ready, seg & 1, DEV_ERR_MMA_WAIT)) break;
+      tc_fence_after();
+      for (int j = t0; j <= t1 && ok; ++j) {
+        const int Jt = J + (j - t0);
+        if (j < t1) {
+          // ---- S[Jt & 1] = Q K_j^T ----
+          const uint32_t d_s = tmem + ((Jt & 1) ? TMEM_S1 : TMEM_S0);
+          for (int c = 0; c < 4 && ok; ++c, ++it) {
+            const int sl = it % DU_NSLOT;
+            if (!wait_all(&ctl->slot_full[sl], (it / DU_NSLOT) & 1, DEV_ERR_MMA_WAIT)) break;
+            tc_fence_after();
+            if (lane == 0) {
+              const uint64_t kd = kdesc0 + (uint64_t)(sl * (DU_SLOT >> 4));
+              const uint64_t qd = qdesc0 + (uint64_t)(c * (DU_SLOT >> 4));
+#pragma unroll
+              for (int k = 0; k < 4; ++k) umma_ss(d_s, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_qk, !(c == 0 && k == 0));
+              if (c == 0 && p.q_lo_dims) {  // low-order part of the rotated channels against the same K sub-tile
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                  umma_ss(d_s, qdesc0 + (uint64_t)(4 * (DU_SLOT >> 4) + k * 2), kd + (uint64_t)(k * 2), idesc_qk, 1);
+              }
+              umma_commit(&ctl->slot_empty[sl]);
+              if (c == 3) umma_commit(&ctl->s_full[Jt & 1]);
+            }
+            __syncwarp();
+          }
+        }
+        if (j > t0 && ok) {
+          // ---- O (+)= P_{j-1} V_{j-1} ----
+          const int jj = j - 1, Jp = Jt - 1;
+          if (!wait_all(&ctl->p_full[Jp & 1], (Jp >> 1) & 1, DEV_ERR_SOFTMAX_WAIT)) break;
+          // the first P V of a segment overwrites O: the previous segment must have read it out
+          if (jj == t0 && seg > 0 && !wait_all(&ctl->o_free, (seg - 1) & 1, DEV_ERR_SOFTMAX_WAIT)) break;
+          tc_fence_after();
+          const uint32_t a_p = tmem + ((Jp & 1) ? TMEM_S1 : TMEM_S0);
+          for (int g = 0; g < 4 && ok; ++g, ++it) {
+            const int sl = it % DU_NSLOT;
+            if (!wait_all(&ctl->slot_full[sl], (it / DU_NSLOT) & 1, DEV_ERR_MMA_WAIT)) break;
+            // keys past the end of the unit may hold anything in V; P is zero there but 0 * NaN
+            // is NaN, so clear those rows before the tensor core reads them
+            const int key_lo = jj * DU_BN + g * 32;
+            if (key_lo + 32 > ui.len) {
+              const int valid = max(0, ui.len - key_lo);
+              for (int idx = lane; idx < 32 * 32; idx += 32) {
+                const int kr = idx >> 5, c16 = idx & 31;
+                if (kr >= valid)
+                  *reinterpret_cast<uint4 *>(ring + sl * DU_SLOT + (c16 >> 3) * 4096 + kr * 128 + (((c16 & 7) ^ (kr & 7)) << 4)) =
+                      make_uint4(0, 0, 0, 0);
+              }
+              fence_proxy_async();
+              __syncwarp();
+            }
+            tc_fence_after();
+            if (lane == 0) {
+              const uint64_t vd = vdesc0 + (uint64_t)(sl * (DU_SLOT >> 4));
+#pragma unroll
+              for (int k = 0; k < 2; ++k) {
+                umma_ts(tmem + TMEM_O, a_p + (g * 2 + k) * 8, vd + (uint64_t)(k * 128), idesc_pv, !(jj == t0 && g == 0 && k == 0));
+                umma_ts(tmem + TMEM_O, a_p + 64 + (g * 2 + k) * 8, vd + (uint64_t)(k * 128), idesc_pv, 1);
+              }
+              umma_commit(&ctl->slot_empty[sl]);
+              if (g == 3) umma_commit(&ctl->o_done[Jp & 1]);
+            }
+            __syncwarp();
+          }
+        }
+      }
+      J += t1 - t0;
+      ++seg;
+      pre += nt;
+      ++u;
+    }
+  } else {
+    // ============ softmax / correction / epilogue: thread = (row, 32-key column group) ============
+    const int wg = (warp - 2) >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const int st_tid = tid - 64;                          // 0 .. 511
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    int u = (int)ctl->part[2];
+    long long pre = ctl->part[1];
+    int J = 0, o_seen = 0;
+    bool ok = true;
+    // P V completions are observed strictly in order (tile t: o_done[t & 1], phase t / 2)
+    auto wait_pv_done = [&](int upto) {
+      while (ok && o_seen <= upto) {
+        ok = wait_or_abort(&ctl->o_done[o_seen & 1], (o_seen >> 1) & 1, abort_flag);
+        ++o_seen;
+      }
+    };
+    while (pre < g1 && u < n_units) {
+      const UnitInfo ui = unit_info(p, u);
+      const int nt = (ui.len + DU_BN - 1) / DU_BN;
+      const int t0 = (int)(max(g0, pre) - pre), t1 = (int)(min(g1, pre + nt) - pre);
+      const int R = ui.ntok * GROUP;
+      const bool whole = (t0 == 0 && t1 == nt);
+      const bool warp_live = (warp & 3) * 32 < R;         // this warp holds at least one real row
+
+      // ---- stage Q for this unit: rows (token b, head hh) -> 6 b + hh, zero padding above R ----
+      for (int idx = st_tid; idx < 128 * 32; idx += DU_SM_THREADS) {
+        const int r = idx >> 5, c16 = idx & 31;           // 8 channels c16*8 .. +7
+        if (p.do_rope && c16 < 8) continue;               // rotary channels are written pair-wise below
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (r < R) {
+          const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + r / GROUP) * p.q_heads + (size_t)ui.kvh * GROUP + r % GROUP;
+          load8<uint16_t>(reinterpret_cast<const uint16_t *>(p.q) + grow * HEAD_DIM + c16 * 8, x);
+        }
+        *reinterpret_cast<uint4 *>(q_smem + q_tile_off(r, c16 * 8)) =
+            make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+      }
+      if (p.do_rope) {
+        for (int idx = st_tid; idx < 128 * ROT_PAIRS; idx += DU_SM_THREADS) {
+          const int r = idx / ROT_PAIRS, i = idx % ROT_PAIRS;  // pair (i, i + 32) of row r
+          float xr = 0.f, yr = 0.f;
+          if (r < R) {
+            const size_t trow = (size_t)ui.s * p.n_new + ui.tok0 + r / GROUP;
+            const uint16_t *src = reinterpret_cast<const uint16_t *>(p.q) + (trow * p.q_heads + (size_t)ui.kvh * GROUP + r % GROUP) * HEAD_DIM;
+            const double x = bf16_bits_to_f32(src[i]), y = bf16_bits_to_f32(src[i + ROT_PAIRS]);
+            const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.pos + ui.tok0 + r / GROUP;
+            double c, sn;
+            rope_sincos_exact(pz, p.rope.inv_freq[i], c, sn);
+            xr = (float)(x * c - y * sn);
+            yr = (float)(x * sn + y * c);
+          }
+          const uint16_t xh = f32_to_bf16_bits(xr), yh = f32_to_bf16_bits(yr);
+          *reinterpret_cast<uint16_t *>(q_smem + q_tile_off(r, i)) = xh;
+          *reinterpret_cast<uint16_t *>(q_smem + q_tile_off(r, i + ROT_PAIRS)) = yh;
+          *reinterpret_cast<uint16_t *>(q_smem + 4 * DU_SLOT + q_tile_off(r, i)) = f32_to_bf16_bits(xr - bf16_bits_to_f32(xh));
+          *reinterpret_cast<uint16_t *>(q_smem + 4 * DU_SLOT + q_tile_off(r, i + ROT_PAIRS)) =
+              f32_to_bf16_bits(yr - bf16_bits_to_f32(yh));
+        }
+      }
+      fence_proxy_async();
+      mbar_arrive(&ctl->q_ready);
+
+      // keys visible to this row; padding rows see none
+      const int lim = row < R ? (p.no_causal ? ui.pos : ui.pos + ui.tok0 + row / GROUP + 1) : 0;
+      const int lim_min = p.no_causal ? ui.pos : ui.pos + ui.tok0 + 1;
+      float m_used = -INFINITY, l_run = 0.f;
+      for (int j = t0; j < t1; ++j) {
+        const int Jt = J + (j - t0);
+        const uint32_t t_s = tmem + lane_sel + ((Jt & 1) ? TMEM_S1 : TMEM_S0);
+        if (ok) ok = wait_or_abort(&ctl->s_full[Jt & 1], (Jt >> 1) & 1, abort_flag);
+        tc_fence_after();
+        uint32_t sr[32];
+        float mx = -INFINITY;
+        if (warp_live) {
+          tmem_ld32(t_s + wg * 32, sr);
+          tmem_wait_ld();
+          const int key0 = j * DU_BN + wg * 32;
+          if (j * DU_BN + DU_BN > lim_min || row >= R) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float v = __uint_as_float(sr[i]);
+              v = (key0 + i < lim) ? v : -INFINITY;
+              sr[i] = __float_as_uint(v);
+              mx = fmaxf(mx, v);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
+          }
+        }
+        ctl->mxbuf[Jt & 1][wg][row] = mx;
+        asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+#pragma unroll
+        for (int w2 = 0; w2 < DU_NWG; ++w2) mx = fmaxf(mx, ctl->mxbuf[Jt & 1][w2][row]);
+        const float m_new = fmaxf(m_used, mx * p.scale_log2);
+        if (__any_sync(0xffffffffu, m_new - m_used > PF_RESCALE_THRESHOLD)) {
+          if (j > t0) {
+            const float alpha = fast_exp2(m_used - m_new);
+            l_run *= alpha;
+            wait_pv_done(Jt - 1);  // O may only be touched once the previous P V has retired
+            if (__all_sync(0xffffffffu, ok)) {
+              tc_fence_after();
+              const uint32_t t_o = tmem + lane_sel + TMEM_O + wg * 64;
+#pragma unroll 1
+              for (int c = 0; c < 2; ++c) {
+                uint32_t orow[32];
+                tmem_ld32(t_o + c * 32, orow);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                tmem_st32(t_o + c * 32, orow);
+              }
+              tmem_wait_st();
+            }
+          }
+          m_used = m_new;
+        }
+        if (warp_live) {
+          const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+          float lsum = 0.f;
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[i]), p.scale_log2, -m_sub));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), p.scale_log2, -m_sub));
+            lsum += p0 + p1;
+            const uint32_t h = pack_bf16(p0, p1);
+            hi[i >> 1] = h;
+            lo[i >> 1] = pack_bf16(p0 - bf16lo(h), p1 - bf16hi(h));
+          }
+          l_run += lsum;
+          tmem_st16(t_s + wg * 16, hi);
+          tmem_st16(t_s + 64 + wg * 16, lo);
+          tmem_wait_st();
+        }
+        tc_fence_before();
+        mbar_arrive(&ctl->p_full[Jt & 1]);
+        if (j > t0) wait_pv_done(Jt - 1);
+      }
+      // ---- end of the segment: read O out, release it, then store the result or a partial ----
+      wait_pv_done(J + (t1 - t0) - 1);
+      ctl->lbuf[wg][row] = l_run;
+      asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+      float l_tot = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < DU_NWG; ++w2) l_tot += ctl->lbuf[w2][row];
+      const bool all_ok = __all_sync(0xffffffffu, ok);
+      const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + row / GROUP) * p.q_heads + (size_t)ui.kvh * GROUP + row % GROUP;
+      const bool final_store = whole && !p.partial_out;
+      float *part_dst = (whole ? p.partial_out + grow * PART_STRIDE
+                               : p.ws + ((size_t)(cta + u) * (p.rb * GROUP) + row) * PART_STRIDE) + wg * 64;
+      if (warp_live && all_ok) {
+        tc_fence_after();
+        const uint32_t t_o = tmem + lane_sel + TMEM_O + wg * 64;
+        const float inv = 1.f / l_tot;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t orow[32];
+          tmem_ld32(t_o + c * 32, orow);
+          tmem_wait_ld();
+          if (row < R) {
+            if (final_store) {
+              const size_t off = grow * HEAD_DIM + wg * 64 + c * 32;
+#pragma unroll
+              for (int v8 = 0; v8 < 4; ++v8) {
+                float o8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(orow[v8 * 8 + e]) * inv;
+                if (p.do_gate) {
+                  float g8[8];
+                  load8<uint16_t>(p.gate + off + v8 * 8, g8);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o8[e] *= sigmoid_fast(g8[e]);
+                }
+                store8<TOut>(reinterpret_cast<TOut *>(p.out) + off + v8 * 8, o8);
+              }
+            } else {
+#pragma unroll
+              for (int v4 = 0; v4 < 8; ++v4)
+                *reinterpret_cast<uint4 *>(part_dst + c * 32 + v4 * 4) =
+                    make_uint4(orow[v4 * 4], orow[v4 * 4 + 1], orow[v4 * 4 + 2], orow[v4 * 4 + 3]);
+            }
+          }
+        }
+        if (row < R && wg == 0) {
+          if (final_store) {
+            if (p.lse) p.lse[grow] = (m_used + log2f(l_tot)) * LN2;
+          } else {
+            part_dst[256] = m_used;
+            part_dst[257] = l_tot;
+          }
+        }
+      }
+      // O has been read (or is abandoned): the next segment's first P V may overwrite it
+      tc_fence_before();
+      mbar_arrive(&ctl->o_free);
+      if (!all_ok) {
+        if (lane == 0) fail(DEV_ERR_SOFTMAX_WAIT);
+        break;
+      }
+      // ---- a unit cut across CTAs is merged by whichever of them arrives last ----
+      if (!whole) {
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+        if (st_tid == 0) ctl->ticket = atomicAdd(&p.cnt[u], 1);
+        asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+        const int c_first = cta_of_tile(pre, total, p.G), c_last = cta_of_tile(pre + nt - 1, total, p.G);
+        int nparts = 0;
+        for (int c = c_first; c <= c_last; ++c) nparts += (total * c / p.G != total * (c + 1) / p.G) ? 1 : 0;
+        if (ctl->ticket == nparts - 1) {
+          __threadfence();
+          for (int r = warp - 2; r < R; r += DU_NWG * 4) merge_unit_row<TOut>(p, u, ui, r, c_first, c_last, total, lane);
+          if (st_tid == 0) p.cnt[u] = 0;
+        }
+      }
+      J += t1 - t0;
+      pre += nt;
+      ++u;
+    }
+  }
+
+  // ---- teardown ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 2000000ull) { }
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace
+
+bool splitkv_umma_usable(int n_new) { return n_new >= 1 && n_new < 64; }
+int splitkv_umma_rb(int n_new) { return n_new < 21 ? n_new : 21; }  // 21 tokens x 6 heads = 126 rows of the tile
+
+int launch_splitkv_umma(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, bool out_is_f32,
+                        cudaStream_t st) {
+  constexpr size_t smem = 1024 + DU_QBYTES + DU_NSLOT * DU_SLOT + sizeof(DecCtl);
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(splitkv_umma_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(splitkv_umma_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return 3;
+    configured[dev] = true;
+  }
+  if (out_is_f32)
+    splitkv_umma_kernel<float><<<p.G, DU_THREADS, smem, st>>>(mk, mv, p);
+  else
+    splitkv_umma_kernel<uint16_t><<<p.G, DU_THREADS, smem, st>>>(mk, mv, p);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : 3;
+}
+
+}  // namespace qwb
