@@ -16,6 +16,13 @@
 
 using namespace qwb;
 
+#ifdef QWB_TIMELINE
+namespace qwb {
+unsigned long long *g_timeline_buf = nullptr;
+int g_timeline_block = 0;
+}  // namespace qwb
+#endif
+
 namespace {
 
 thread_local char g_cuda_err[256] = "";
@@ -255,6 +262,7 @@ int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.rb = splitkv_umma_rb(c.n_new);
   p.nblk = (c.n_new + p.rb - 1) / p.rb;
+  splitkv_umma_layout(p.rb, &p.q_rows_pad, &p.nslot);
   const long long n_units = (long long)c.n_seq * p.nblk * c.kv_heads;
   if (n_units > (1 << 24)) return QW_ERR_SHAPE;
   const long long max_slots = (long long)(c.ws_floats / splitkv_slot_floats(p.rb));
@@ -271,6 +279,9 @@ int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   if (rc) return rc;
   rc = make_rowmajor_map(&mv, c.vc, c.cache_rows, c.kv_heads * HEAD_DIM, 32);
   if (rc) return rc;
+#ifdef QWB_TIMELINE
+  p.dbg = qwb::g_timeline_buf; p.dbg_block = qwb::g_timeline_block;
+#endif
   prof_mark(0, st);
   rc = launch_splitkv_umma(mk, mv, p, c.out_is_f32, st);
   prof_mark(1, st);
@@ -403,10 +414,6 @@ int noalloc_scratch_address(float **out) {
 }  // namespace
 
 #ifdef QWB_TIMELINE
-namespace qwb {
-unsigned long long *g_timeline_buf = nullptr;
-int g_timeline_block = 0;
-}  // namespace qwb
 extern "C" void qw_debug_set_timeline(unsigned long long *buf, int block) {
   qwb::g_timeline_buf = buf;
   qwb::g_timeline_block = block;

@@ -116,7 +116,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 
   if (warp == 0) {
     // =============================== TMA producer ===========================================
-    if (lane == 0) {
+    if (elect_one()) {
       mbar_expect_tx(&ctl->q_full, 4 * PF_SLOT);
       const int qrow = s * p.n_new + q0;
 #pragma unroll
@@ -183,7 +183,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) { if (lane == 0) { if (!*abort_flag && p.status) *p.status = DEV_ERR_MMA_WAIT; *abort_flag = 1; } break; }
           tc_fence_after();
-          if (lane == 0) {
+          if (elect_one()) {
             const uint64_t kd = kdesc0 + (uint64_t)(sl * (PF_SLOT >> 4));
             const uint64_t qd = qdesc0 + (uint64_t)(c * (PF_SLOT >> 4));
 #pragma unroll
@@ -227,7 +227,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
             __syncwarp();
           }
           tc_fence_after();
-          if (lane == 0) {
+          if (elect_one()) {
             const uint64_t vd = vdesc0 + (uint64_t)(sl * (PF_SLOT >> 4));
 #pragma unroll
             for (int k = 0; k < 2; ++k) {

@@ -223,7 +223,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
   if (warp == 0) {
     // =============================== TMA producer (each CTA loads its halves) ================
     int producer_ok = 1;
-    if (run && lane == 0) {
+    if (run && elect_one()) {
       mbar_expect_tx(&ctl->q_full, 4 * P2_SLOT);
       const int qrow = s * p.n_new + q0;
 #pragma unroll
@@ -284,7 +284,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         const int sl = itv % P2_NSLOT;
         if (g == 0) ok = wait_v_slots_free(nt - 1);
         ok = __all_sync(0xffffffffu, ok);
-        if (ok && lane == 0) {
+        if (ok && elect_one()) {
           mbar_expect_tx(&ctl->fix_bar, P2_SLOT);
           const int vrow = (int)(crow + (nt - 1) * P2_BN + g * 64);
 #pragma unroll
@@ -314,7 +314,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
     // A tcgen05.mma of this shape occupies the tensor pipe for only ~64 cycles, so the issuing
     // thread must not spend longer than that per instruction: descriptors are built once and
     // advanced by adding the (16-byte unit) offset to their start-address field.
-    if (run && leader && lane == 0) {
+    if (run && leader && elect_one()) {
       const uint32_t idesc_qk = make_idesc(256, 128, 1, 1, 0, 0);
       const uint32_t idesc_pv = make_idesc(256, 256, 1, 1, 0, 1);
       const uint64_t qdesc0 = smem_desc(smem_u32(q_smem), 16, 1024);

@@ -48,6 +48,10 @@ struct SplitKVParams {
   int q_lo_dims;          // 0, 64 or 256: leading dims that carry a bf16 "lo" part
   float scale_log2;       // softmax scale * log2(e)
   int do_rope, do_gate;
+  int q_rows_pad;         // tcgen05 kernel: rows of the Q tile that really exist in shared memory (32, 64 or 128)
+  int nslot;              // tcgen05 kernel: 16 KB ring slots that fit beside that Q tile
+  unsigned long long *dbg;  // timeline probe (only written when built with QWB_TIMELINE)
+  int dbg_block;
   int no_causal;          // every row sees exactly pos[s] keys (a KV sub-range without the new rows)
   RopeTable rope;
 };

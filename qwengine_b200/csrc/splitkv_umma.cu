@@ -29,15 +29,15 @@ namespace {
 
 constexpr int DU_BN = 128;                 // keys per tile
 constexpr int DU_SLOT = 16384;
-constexpr int DU_NSLOT = 8;
-constexpr int DU_QBYTES = 5 * DU_SLOT;     // four 64-channel sub-tiles of 128 rows + the rotary "lo" sub-tile
+constexpr int DU_MAX_SLOT = 13;            // ring slots when the Q tile is smallest
+constexpr int DU_SMEM_TOTAL = 232448 - 1024;   // dynamic shared memory left after the alignment slack
 constexpr int DU_NWG = 4;
 constexpr int DU_SM_THREADS = DU_NWG * 128;
 constexpr int DU_THREADS = 64 + DU_SM_THREADS;
 
 struct DecCtl {
   uint64_t q_ready, o_free, s_full[2], p_full[2], o_done[2];
-  uint64_t slot_full[DU_NSLOT], slot_empty[DU_NSLOT];
+  uint64_t slot_full[DU_MAX_SLOT], slot_empty[DU_MAX_SLOT];
   uint32_t tmem_base;
   volatile int abort_flag;
   volatile int ticket;
@@ -46,10 +46,16 @@ struct DecCtl {
   float lbuf[DU_NWG][128];
 };
 
-// Byte offset of element (row, d) of the 128-row Q tile: 64-channel sub-tiles of 128-byte rows,
-// 16-byte column XOR (row & 7) -- the K-major 128-byte-swizzle operand layout.
-__device__ __forceinline__ uint32_t q_tile_off(int row, int d) {
-  return (uint32_t)((d >> 6) * DU_SLOT + row * 128 + ((((d >> 3) & 7) ^ (row & 7)) << 4) + ((d & 7) << 1));
+// Byte offset of element (row, d) of the Q tile: 64-channel sub-tiles (sub_bytes apart) of 128-byte
+// rows, 16-byte column XOR (row & 7) -- the K-major 128-byte-swizzle operand layout.
+//
+// Only the first q_rows_pad (32, 64 or 128) rows of the 128-row MMA tile exist in shared memory.
+// The operand descriptor still spans 128 rows; the rows past q_rows_pad read whatever follows (the
+// next sub-tile, the ring), which is valid shared memory whose contents only reach accumulator rows
+// that nobody reads.  That shrinks Q from 80 KB to 20 KB for decode and verify and gives the bytes
+// to the K/V ring, where an HBM-bound kernel needs them (bytes in flight = bandwidth x latency).
+__device__ __forceinline__ uint32_t q_tile_off(int row, int d, int sub_bytes) {
+  return (uint32_t)((d >> 6) * sub_bytes + row * 128 + ((((d >> 3) & 7) ^ (row & 7)) << 4) + ((d & 7) << 1));
 }
 
 template <typename TOut>
@@ -58,11 +64,14 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
                     const __grid_constant__ SplitKVParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int QSUB = p.q_rows_pad * 128;      // bytes of one 64-channel Q sub-tile
+  const int DU_NSLOT = p.nslot;
   uint8_t *q_smem = smem;
-  uint8_t *ring = smem + DU_QBYTES;
-  DecCtl *ctl = reinterpret_cast<DecCtl *>(ring + DU_NSLOT * DU_SLOT);
+  uint8_t *ring = smem + 5 * QSUB;          // four sub-tiles + the rotary "lo" sub-tile; a multiple of 1 KB
+  DecCtl *ctl = reinterpret_cast<DecCtl *>(smem + DU_SMEM_TOTAL - sizeof(DecCtl));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) QWB_TL(30, 0);
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
   const int cta = blockIdx.x;
 
@@ -74,7 +83,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       mbar_init(&ctl->p_full[i], DU_SM_THREADS);
       mbar_init(&ctl->o_done[i], 1);
     }
-    for (int i = 0; i < DU_NSLOT; ++i) { mbar_init(&ctl->slot_full[i], 1); mbar_init(&ctl->slot_empty[i], 1); }
+    for (int i = 0; i < DU_MAX_SLOT; ++i) { mbar_init(&ctl->slot_full[i], 1); mbar_init(&ctl->slot_empty[i], 1); }
     ctl->abort_flag = (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) ? 1 : 0;
     fence_barrier_init();
     prefetch_tensormap(&mapK);
@@ -99,6 +108,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
+  if (tid == 0) QWB_TL(30, 2);
   volatile int *abort_flag = &ctl->abort_flag;
   auto fail = [&](int code) {
     if (!*abort_flag && p.status) *p.status = code;
@@ -109,20 +119,23 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     // =============================== TMA producer ===========================================
     // Per segment the slot stream is  K_t0 | K_t0+1 V_t0 | ... | V_t1-1 ; segments follow each
     // other without a gap.  A K slot is one 64-channel sub-tile of 128 keys, a V slot 32 keys x 256.
-    if (lane == 0) {
+    if (elect_one()) {
       int u = (int)ctl->part[2];
       long long pre = ctl->part[1];
-      uint32_t it = 0;
-      bool ok = true;
+      int sl = 0;            // ring position: slot, and the parity of the slot's current use
+      uint32_t ph = 0;
+      bool wrapped = false, ok = true;
       auto slot_ready = [&]() -> bool {
-        const int sl = it % DU_NSLOT;
-        if (it >= DU_NSLOT && !wait_or_abort(&ctl->slot_empty[sl], ((it / DU_NSLOT) - 1) & 1, abort_flag)) {
+        if (wrapped && !wait_or_abort(&ctl->slot_empty[sl], ph ^ 1, abort_flag)) {
           fail(DEV_ERR_EMPTY_WAIT);
           ok = false;
           return false;
         }
         mbar_expect_tx(&ctl->slot_full[sl], DU_SLOT);
         return true;
+      };
+      auto advance = [&]() {
+        if (++sl == DU_NSLOT) { sl = 0; ph ^= 1; wrapped = true; }
       };
       while (pre < g1 && u < n_units && ok) {
         const UnitInfo ui = unit_info(p, u);
@@ -131,23 +144,23 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         const long long row0 = p.cache_row ? p.cache_row[ui.s] : 0;
         for (int j = t0; j <= t1 && ok; ++j) {
           if (j < t1) {
+            QWB_TL(10, j - t0);
             for (int c = 0; c < 4 && ok; ++c) {
               if (!slot_ready()) break;
-              const int sl = it % DU_NSLOT;
               tma_load_2d(ring + sl * DU_SLOT, &mapK, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
                           (int)(row0 + (long long)j * DU_BN));
-              ++it;
+              advance();
             }
           }
           if (j > t0 && ok) {
+            QWB_TL(11, j - 1 - t0);
             for (int g = 0; g < 4 && ok; ++g) {
               if (!slot_ready()) break;
-              const int sl = it % DU_NSLOT;
 #pragma unroll
               for (int c = 0; c < 4; ++c)  // 32 keys x 64 channels each, channel atoms 4 KB apart
                 tma_load_2d(ring + sl * DU_SLOT + c * 4096, &mapV, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
                             (int)(row0 + (long long)(j - 1) * DU_BN + g * 32));
-              ++it;
+              advance();
             }
           }
         }
@@ -157,26 +170,31 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ==============================================
-    // The whole warp walks the tile sequence (so that it can clear ragged V rows together); lane 0
-    // issues.  J counts tiles over all segments of this CTA: S / P buffer J & 1, barrier phase J >> 1.
+    // The whole warp walks the tile sequence (so that it can clear ragged V rows together); the
+    // elected lane issues.  J counts tiles over all segments of this CTA: S / P buffer J & 1,
+    // barrier phase J >> 1.
     const uint32_t idesc_qk = make_idesc(128, 128, 1, 1, 0, 0);
     const uint32_t idesc_pv = make_idesc(128, 256, 1, 1, 0, 1);
     const uint64_t qdesc0 = smem_desc(smem_u32(q_smem), 16, 1024);
     const uint64_t kdesc0 = smem_desc(smem_u32(ring), 16, 1024);
     const uint64_t vdesc0 = smem_desc(smem_u32(ring), 4096, 1024);
+    const uint32_t qsub16 = (uint32_t)(QSUB >> 4);
     int u = (int)ctl->part[2];
     long long pre = ctl->part[1];
-    uint32_t it = 0;
+    int sl = 0;
+    uint32_t ph = 0;
     int J = 0, seg = 0;
     bool ok = true;
     auto wait_all = [&](uint64_t *bar, uint32_t parity, int code) {
-      bool got = wait_or_abort(bar, parity, abort_flag);
-      got = __all_sync(0xffffffffu, got);
+      const bool got = __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag));
       if (!got) {
         if (lane == 0) fail(code);
         ok = false;
       }
       return got;
+    };
+    auto advance = [&]() {
+      if (++sl == DU_NSLOT) { sl = 0; ph ^= 1; }
     };
     while (pre < g1 && u < n_units && ok) {
       const UnitInfo ui = unit_info(p, u);
@@ -189,37 +207,39 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         if (j < t1) {
           // ---- S[Jt & 1] = Q K_j^T ----
           const uint32_t d_s = tmem + ((Jt & 1) ? TMEM_S1 : TMEM_S0);
-          for (int c = 0; c < 4 && ok; ++c, ++it) {
-            const int sl = it % DU_NSLOT;
-            if (!wait_all(&ctl->slot_full[sl], (it / DU_NSLOT) & 1, DEV_ERR_MMA_WAIT)) break;
+          if (lane == 0) QWB_TL(0, Jt);
+          for (int c = 0; c < 4 && ok; ++c) {
+            if (!wait_all(&ctl->slot_full[sl], ph, DEV_ERR_MMA_WAIT)) break;
             tc_fence_after();
-            if (lane == 0) {
+            if (elect_one()) {
               const uint64_t kd = kdesc0 + (uint64_t)(sl * (DU_SLOT >> 4));
-              const uint64_t qd = qdesc0 + (uint64_t)(c * (DU_SLOT >> 4));
+              const uint64_t qd = qdesc0 + (uint64_t)(c * qsub16);
 #pragma unroll
-              for (int k = 0; k < 4; ++k) umma_ss(d_s, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_qk, !(c == 0 && k == 0));
+              for (int k = 0; k < 4; ++k) umma_ss(d_s, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_qk, (c | k) != 0);
               if (c == 0 && p.q_lo_dims) {  // low-order part of the rotated channels against the same K sub-tile
+                const uint64_t ql = qdesc0 + (uint64_t)(4 * qsub16);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                  umma_ss(d_s, qdesc0 + (uint64_t)(4 * (DU_SLOT >> 4) + k * 2), kd + (uint64_t)(k * 2), idesc_qk, 1);
+                for (int k = 0; k < 4; ++k) umma_ss(d_s, ql + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_qk, 1);
               }
               umma_commit(&ctl->slot_empty[sl]);
               if (c == 3) umma_commit(&ctl->s_full[Jt & 1]);
             }
             __syncwarp();
+            advance();
           }
         }
         if (j > t0 && ok) {
+          if (lane == 0) QWB_TL(1, Jt);
           // ---- O (+)= P_{j-1} V_{j-1} ----
           const int jj = j - 1, Jp = Jt - 1;
           if (!wait_all(&ctl->p_full[Jp & 1], (Jp >> 1) & 1, DEV_ERR_SOFTMAX_WAIT)) break;
           // the first P V of a segment overwrites O: the previous segment must have read it out
           if (jj == t0 && seg > 0 && !wait_all(&ctl->o_free, (seg - 1) & 1, DEV_ERR_SOFTMAX_WAIT)) break;
           tc_fence_after();
+          if (lane == 0) QWB_TL(2, Jp);
           const uint32_t a_p = tmem + ((Jp & 1) ? TMEM_S1 : TMEM_S0);
-          for (int g = 0; g < 4 && ok; ++g, ++it) {
-            const int sl = it % DU_NSLOT;
-            if (!wait_all(&ctl->slot_full[sl], (it / DU_NSLOT) & 1, DEV_ERR_MMA_WAIT)) break;
+          for (int g = 0; g < 4 && ok; ++g) {
+            if (!wait_all(&ctl->slot_full[sl], ph, DEV_ERR_MMA_WAIT)) break;
             // keys past the end of the unit may hold anything in V; P is zero there but 0 * NaN
             // is NaN, so clear those rows before the tensor core reads them
             const int key_lo = jj * DU_BN + g * 32;
@@ -235,18 +255,21 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
               __syncwarp();
             }
             tc_fence_after();
-            if (lane == 0) {
+            if (elect_one()) {
               const uint64_t vd = vdesc0 + (uint64_t)(sl * (DU_SLOT >> 4));
+              const uint32_t first = (uint32_t)(jj != t0) | (uint32_t)g;
 #pragma unroll
               for (int k = 0; k < 2; ++k) {
-                umma_ts(tmem + TMEM_O, a_p + (g * 2 + k) * 8, vd + (uint64_t)(k * 128), idesc_pv, !(jj == t0 && g == 0 && k == 0));
+                umma_ts(tmem + TMEM_O, a_p + (g * 2 + k) * 8, vd + (uint64_t)(k * 128), idesc_pv, first | (uint32_t)k);
                 umma_ts(tmem + TMEM_O, a_p + 64 + (g * 2 + k) * 8, vd + (uint64_t)(k * 128), idesc_pv, 1);
               }
               umma_commit(&ctl->slot_empty[sl]);
               if (g == 3) umma_commit(&ctl->o_done[Jp & 1]);
             }
             __syncwarp();
+            advance();
           }
+          if (lane == 0) QWB_TL(3, Jp);
         }
       }
       J += t1 - t0;
@@ -265,6 +288,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     int J = 0, o_seen = 0;
     bool ok = true;
     // P V completions are observed strictly in order (tile t: o_done[t & 1], phase t / 2)
+    int segx = 0;
     auto wait_pv_done = [&](int upto) {
       while (ok && o_seen <= upto) {
         ok = wait_or_abort(&ctl->o_done[o_seen & 1], (o_seen >> 1) & 1, abort_flag);
@@ -279,8 +303,9 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       const bool whole = (t0 == 0 && t1 == nt);
       const bool warp_live = (warp & 3) * 32 < R;         // this warp holds at least one real row
 
+      if (tid == 64) QWB_TL(30, 3 + 6 * segx);
       // ---- stage Q for this unit: rows (token b, head hh) -> 6 b + hh, zero padding above R ----
-      for (int idx = st_tid; idx < 128 * 32; idx += DU_SM_THREADS) {
+      for (int idx = st_tid; idx < p.q_rows_pad * 32; idx += DU_SM_THREADS) {
         const int r = idx >> 5, c16 = idx & 31;           // 8 channels c16*8 .. +7
         if (p.do_rope && c16 < 8) continue;               // rotary channels are written pair-wise below
         float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -288,11 +313,11 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + r / GROUP) * p.q_heads + (size_t)ui.kvh * GROUP + r % GROUP;
           load8<uint16_t>(reinterpret_cast<const uint16_t *>(p.q) + grow * HEAD_DIM + c16 * 8, x);
         }
-        *reinterpret_cast<uint4 *>(q_smem + q_tile_off(r, c16 * 8)) =
+        *reinterpret_cast<uint4 *>(q_smem + q_tile_off(r, c16 * 8, QSUB)) =
             make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
       }
       if (p.do_rope) {
-        for (int idx = st_tid; idx < 128 * ROT_PAIRS; idx += DU_SM_THREADS) {
+        for (int idx = st_tid; idx < p.q_rows_pad * ROT_PAIRS; idx += DU_SM_THREADS) {
           const int r = idx / ROT_PAIRS, i = idx % ROT_PAIRS;  // pair (i, i + 32) of row r
           float xr = 0.f, yr = 0.f;
           if (r < R) {
@@ -306,15 +331,16 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
             yr = (float)(x * sn + y * c);
           }
           const uint16_t xh = f32_to_bf16_bits(xr), yh = f32_to_bf16_bits(yr);
-          *reinterpret_cast<uint16_t *>(q_smem + q_tile_off(r, i)) = xh;
-          *reinterpret_cast<uint16_t *>(q_smem + q_tile_off(r, i + ROT_PAIRS)) = yh;
-          *reinterpret_cast<uint16_t *>(q_smem + 4 * DU_SLOT + q_tile_off(r, i)) = f32_to_bf16_bits(xr - bf16_bits_to_f32(xh));
-          *reinterpret_cast<uint16_t *>(q_smem + 4 * DU_SLOT + q_tile_off(r, i + ROT_PAIRS)) =
+          *reinterpret_cast<uint16_t *>(q_smem + q_tile_off(r, i, QSUB)) = xh;
+          *reinterpret_cast<uint16_t *>(q_smem + q_tile_off(r, i + ROT_PAIRS, QSUB)) = yh;
+          *reinterpret_cast<uint16_t *>(q_smem + 4 * QSUB + q_tile_off(r, i, QSUB)) = f32_to_bf16_bits(xr - bf16_bits_to_f32(xh));
+          *reinterpret_cast<uint16_t *>(q_smem + 4 * QSUB + q_tile_off(r, i + ROT_PAIRS, QSUB)) =
               f32_to_bf16_bits(yr - bf16_bits_to_f32(yh));
         }
       }
       fence_proxy_async();
       mbar_arrive(&ctl->q_ready);
+      if (tid == 64) QWB_TL(30, 4 + 6 * segx);
 
       // keys visible to this row; padding rows see none
       const int lim = row < R ? (p.no_causal ? ui.pos : ui.pos + ui.tok0 + row / GROUP + 1) : 0;
@@ -323,7 +349,9 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       for (int j = t0; j < t1; ++j) {
         const int Jt = J + (j - t0);
         const uint32_t t_s = tmem + lane_sel + ((Jt & 1) ? TMEM_S1 : TMEM_S0);
+        if (tid == 64) QWB_TL(4, Jt);
         if (ok) ok = wait_or_abort(&ctl->s_full[Jt & 1], (Jt >> 1) & 1, abort_flag);
+        if (tid == 64) QWB_TL(5, Jt);
         tc_fence_after();
         uint32_t sr[32];
         float mx = -INFINITY;
@@ -344,8 +372,10 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
             for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
           }
         }
+        if (tid == 64) QWB_TL(6, Jt);
         ctl->mxbuf[Jt & 1][wg][row] = mx;
         asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+        if (tid == 64) QWB_TL(7, Jt);
 #pragma unroll
         for (int w2 = 0; w2 < DU_NWG; ++w2) mx = fmaxf(mx, ctl->mxbuf[Jt & 1][w2][row]);
         const float m_new = fmaxf(m_used, mx * p.scale_log2);
@@ -391,10 +421,13 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         }
         tc_fence_before();
         mbar_arrive(&ctl->p_full[Jt & 1]);
+        if (tid == 64) QWB_TL(8, Jt);
         if (j > t0) wait_pv_done(Jt - 1);
+        if (tid == 64) QWB_TL(9, Jt);
       }
       // ---- end of the segment: read O out, release it, then store the result or a partial ----
       wait_pv_done(J + (t1 - t0) - 1);
+      if (tid == 64) QWB_TL(30, 5 + 6 * segx);
       ctl->lbuf[wg][row] = l_run;
       asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
       float l_tot = 0.f;
@@ -450,6 +483,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       // O has been read (or is abandoned): the next segment's first P V may overwrite it
       tc_fence_before();
       mbar_arrive(&ctl->o_free);
+      if (tid == 64) QWB_TL(30, 6 + 6 * segx);
       if (!all_ok) {
         if (lane == 0) fail(DEV_ERR_SOFTMAX_WAIT);
         break;
@@ -469,6 +503,8 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           if (st_tid == 0) p.cnt[u] = 0;
         }
       }
+      if (tid == 64) QWB_TL(30, 7 + 6 * segx);
+      ++segx;
       J += t1 - t0;
       pre += nt;
       ++u;
@@ -476,6 +512,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   }
 
   // ---- teardown ----
+  if (tid == 64) QWB_TL(30, 40);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -492,10 +529,17 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
 
 bool splitkv_umma_usable(int n_new) { return n_new >= 1 && n_new < 64; }
 int splitkv_umma_rb(int n_new) { return n_new < 21 ? n_new : 21; }  // 21 tokens x 6 heads = 126 rows of the tile
+void splitkv_umma_layout(int rb, int *q_rows_pad, int *nslot) {
+  const int rows = rb * GROUP;
+  *q_rows_pad = rows <= 32 ? 32 : (rows <= 64 ? 64 : 128);
+  const int avail = DU_SMEM_TOTAL - (int)sizeof(DecCtl) - 5 * *q_rows_pad * 128;
+  int n = avail / DU_SLOT;
+  *nslot = n > DU_MAX_SLOT ? DU_MAX_SLOT : n;
+}
 
 int launch_splitkv_umma(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, bool out_is_f32,
                         cudaStream_t st) {
-  constexpr size_t smem = 1024 + DU_QBYTES + DU_NSLOT * DU_SLOT + sizeof(DecCtl);
+  constexpr size_t smem = 1024 + DU_SMEM_TOTAL;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
