@@ -157,6 +157,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   }
   return false;
 }
+// 16-byte asynchronous copy global -> shared (no registers held while in flight) and its wait.
+__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

@@ -93,13 +93,14 @@ __device__ __forceinline__ long long warp_total_tiles(const SplitKVParams &p, in
 // Warp-cooperative: the unit containing flat tile g and the flat index of that unit's tile 0.
 template <int TK = SK_TK>
 __device__ __forceinline__ void warp_find_unit(const SplitKVParams &p, int n_units, int lane, long long g,
-                                               int &u_out, long long &pre_out) {
+                                               int &u_out, long long &pre_out, int extra = 0) {
   long long carry = 0;
   u_out = n_units;
   pre_out = 0;
   for (int base = 0; base < n_units; base += 32) {
     const int u = base + lane;
-    const long long mine = u < n_units ? unit_tiles<TK>(p, u) : 0;
+    long long mine = u < n_units ? unit_tiles<TK>(p, u) : 0;
+    if (mine > 0) mine += extra;  // list entries that precede the unit's tiles (see splitkv_umma.cu)
     long long inc = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -143,45 +144,11 @@ __device__ __forceinline__ uint32_t q_hi_off(int row, int d) {
   return (uint32_t)(row * 512 + ((c16 ^ (row & 7)) << 4) + ((d & 7) << 1));
 }
 
-// Merges the partials of one row of unit u, written by the CTAs c_first..c_last that own tiles
-// of the unit, in CTA order (fixed order => bit-stable), then normalises, gates and stores.
-// One warp per row, lane = 8 channels.  Used by the merge kernel and, when arrival counters are
-// available, by whichever CTA finishes the unit last.
+// Last step of a merge: the row's partial (for a KV-range split over GPUs) or its normalised, gated
+// output and log-sum-exp.  lane = 8 channels.
 template <typename TOut>
-__device__ __forceinline__ void merge_unit_row(const SplitKVParams &p, int u, const UnitInfo &ui, int row, int c_first,
-                                               int c_last, long long total, int lane) {
-  // Partials are fetched four at a time with all their loads in flight together (a unit is
-  // usually cut into two to four pieces, so this is one L2 round trip) and folded in with a
-  // running maximum, strictly in CTA order.
-  float mg = -INFINITY, lg = 0.f;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int c0 = c_first; c0 <= c_last; c0 += 4) {
-    float mv[4], lv[4];
-    float4 av[4], bv[4];
-    bool live[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int c = c0 + k;
-      live[k] = c <= c_last && (total * c / p.G != total * (c + 1) / p.G);  // CTAs without tiles wrote nothing
-      const float *src = p.ws + ((size_t)((live[k] ? c : c_first) + u) * (p.rb * GROUP) + row) * PART_STRIDE;
-      mv[k] = __ldcg(src + 256);
-      lv[k] = __ldcg(src + 257);
-      av[k] = __ldcg(reinterpret_cast<const float4 *>(src + lane * 8));
-      bv[k] = __ldcg(reinterpret_cast<const float4 *>(src + lane * 8 + 4));
-    }
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      if (!live[k] || !(lv[k] > 0.f)) continue;
-      const float m_new = fmaxf(mg, mv[k]);
-      const float f_old = fast_exp2(mg - m_new), f = fast_exp2(mv[k] - m_new);  // mg = -inf gives f_old = 0
-      mg = m_new;
-      lg = lg * f_old + lv[k] * f;
-      acc[0] = acc[0] * f_old + av[k].x * f; acc[1] = acc[1] * f_old + av[k].y * f;
-      acc[2] = acc[2] * f_old + av[k].z * f; acc[3] = acc[3] * f_old + av[k].w * f;
-      acc[4] = acc[4] * f_old + bv[k].x * f; acc[5] = acc[5] * f_old + bv[k].y * f;
-      acc[6] = acc[6] * f_old + bv[k].z * f; acc[7] = acc[7] * f_old + bv[k].w * f;
-    }
-  }
+__device__ __forceinline__ void merge_finish(const SplitKVParams &p, const UnitInfo &ui, int row, int lane, float mg,
+                                             float lg, float (&acc)[8]) {
   const int b = row / GROUP, hh = row % GROUP;
   const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
   if (p.partial_out) {
@@ -206,6 +173,63 @@ __device__ __forceinline__ void merge_unit_row(const SplitKVParams &p, int u, co
   }
   store8<TOut>(reinterpret_cast<TOut *>(p.out) + grow * HEAD_DIM + lane * 8, acc);
   if (lane == 0 && p.lse) p.lse[grow] = (mg + log2f(lg)) * LN2;
+}
+
+// Merges the partials of one row of unit u, written by the CTAs c_first..c_last that own tiles
+// of the unit, in CTA order (fixed order => bit-stable), then normalises, gates and stores.
+// One warp per row, lane = 8 channels.  Used by the merge kernel and, when arrival counters are
+// available, by whichever CTA finishes the unit last.
+template <typename TOut>
+__device__ __forceinline__ void merge_unit_row(const SplitKVParams &p, int u, const UnitInfo &ui, int row, int c_first,
+                                               int c_last, long long total, int lane, int G,
+                                               const volatile uint8_t *live_of = nullptr) {
+  // Partials are fetched four at a time with all their loads in flight together (a unit is
+  // usually cut into two to four pieces, so this is one L2 round trip) and folded in with a
+  // running maximum, strictly in CTA order.
+  float mg = -INFINITY, lg = 0.f;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#ifdef QWB_TIMELINE
+  long long tl0 = clock64(); int tlb = 0;
+#endif
+  for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+    float mv[4], lv[4];
+    float4 av[4], bv[4];
+    bool live[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = c0 + k;
+      // CTAs without tiles wrote nothing; live_of, when given, holds that test for c_first .. c_last
+      // (64-bit divisions are slow enough to dominate a merge of many parts)
+      live[k] = c <= c_last && (live_of ? live_of[c - c_first] != 0 : (total * c / G != total * (c + 1) / G));
+      const float *src = p.ws + ((size_t)((live[k] ? c : c_first) + u) * (p.rb * GROUP) + row) * PART_STRIDE;
+      mv[k] = __ldcg(src + 256);
+      lv[k] = __ldcg(src + 257);
+      av[k] = __ldcg(reinterpret_cast<const float4 *>(src + lane * 8));
+      bv[k] = __ldcg(reinterpret_cast<const float4 *>(src + lane * 8 + 4));
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (!live[k] || !(lv[k] > 0.f)) continue;
+      const float m_new = fmaxf(mg, mv[k]);
+      const float f_old = fast_exp2(mg - m_new), f = fast_exp2(mv[k] - m_new);  // mg = -inf gives f_old = 0
+      mg = m_new;
+      lg = lg * f_old + lv[k] * f;
+      acc[0] = acc[0] * f_old + av[k].x * f; acc[1] = acc[1] * f_old + av[k].y * f;
+      acc[2] = acc[2] * f_old + av[k].z * f; acc[3] = acc[3] * f_old + av[k].w * f;
+      acc[4] = acc[4] * f_old + bv[k].x * f; acc[5] = acc[5] * f_old + bv[k].y * f;
+      acc[6] = acc[6] * f_old + bv[k].z * f; acc[7] = acc[7] * f_old + bv[k].w * f;
+    }
+#ifdef QWB_TIMELINE
+    if (p.dbg && (int)blockIdx.x == p.dbg_block && threadIdx.x == 64 && tlb < 8) { p.dbg[28 * 64 + 8 * (row >= 16) + tlb] = clock64() - tl0 + (acc[0] == 12345.f); ++tlb; }
+#endif
+  }
+#ifdef QWB_TIMELINE
+  if (p.dbg && (int)blockIdx.x == p.dbg_block && threadIdx.x == 64) p.dbg[28 * 64 + 16 + (row >= 16)] = clock64() - tl0;
+#endif
+  merge_finish<TOut>(p, ui, row, lane, mg, lg, acc);
+#ifdef QWB_TIMELINE
+  if (p.dbg && (int)blockIdx.x == p.dbg_block && threadIdx.x == 64) p.dbg[28 * 64 + 18 + (row >= 16)] = clock64() - tl0;
+#endif
 }
 
 // FOLD = false: a dedicated producer warp (warp NCW).  FOLD = true: lane 0 of consumer warp 0 also
@@ -659,7 +683,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       for (int c = c_first; c <= c_last; ++c) nparts += (total * c / p.G != total * (c + 1) / p.G) ? 1 : 0;
       if (*ticket == nparts - 1) {
         __threadfence();
-        for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane);
+        for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, p.G);
         if (tid == 0) p.cnt[u] = 0;  // leave the counter clean for a caller that does not reset it
       }
     }
@@ -688,7 +712,7 @@ __global__ void __launch_bounds__(256) splitkv_merge_kernel(const __grid_constan
   const int c_first = cta_of_tile(pre, total, p.G), c_last = cta_of_tile(pre + nt - 1, total, p.G);
   if (c_first == c_last) return;  // the main kernel already wrote this unit
   const int R = ui.ntok * GROUP;
-  for (int row = warp; row < R; row += 8) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane);
+  for (int row = warp; row < R; row += 8) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, p.G);
 }
 
 // Merge n_parts partial sets [n_parts][n][PART_STRIDE] (n = rows * q_heads) in index order, then

@@ -32,6 +32,9 @@ constexpr int DU_SLOT = 16384;
 constexpr int DU_MAX_SLOT = 13;            // ring slots when the Q tile is smallest
 constexpr int DU_SMEM_TOTAL = 232448 - 1024;   // dynamic shared memory left after the alignment slack
 constexpr int DU_NWG = 4;
+constexpr int DU_MAX_PARTS = 256;         // CTAs of one unit whose liveness is tabulated for the merge
+constexpr bool DU_STAGED_MERGE = false;
+constexpr int DU_SWITCH_TILES = 4;        // least number of tiles of time a CTA loses where its slice crosses into the next unit
 constexpr int DU_SM_THREADS = DU_NWG * 128;
 constexpr int DU_THREADS = 64 + DU_SM_THREADS;
 
@@ -40,8 +43,11 @@ struct DecCtl {
   uint64_t slot_full[DU_MAX_SLOT], slot_empty[DU_MAX_SLOT];
   uint32_t tmem_base;
   volatile int abort_flag;
-  volatile int ticket;
-  long long part[3];             // total tiles, flat index of the first unit's tile 0, first unit
+  volatile int ticket[2];
+  volatile int merge_go;
+  volatile int merge_parts[2];   // CTAs that hold a part of each pending unit
+  volatile uint8_t merge_live[2][DU_MAX_PARTS];
+  long long part[5];             // total tiles, flat index of the first unit's tile 0, first unit, CTAs in use, lead entries per unit
   float mxbuf[2][DU_NWG][128];
   float lbuf[DU_NWG][128];
 };
@@ -71,7 +77,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   DecCtl *ctl = reinterpret_cast<DecCtl *>(smem + DU_SMEM_TOTAL - sizeof(DecCtl));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) QWB_TL(30, 0);
+  if (tid == 0) { QWB_TL(30, 0); QWB_TLB(0); }
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
   const int cta = blockIdx.x;
 
@@ -90,17 +96,45 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     prefetch_tensormap(&mapV);
   }
   if (warp == 2) {
-    const long long total = warp_total_tiles<DU_BN>(p, n_units, lane);
-    const long long g0 = total * cta / p.G;
-    int u0; long long pre0;
-    warp_find_unit<DU_BN>(p, n_units, lane, g0, u0, pre0);
-    if (lane == 0) { ctl->part[0] = total; ctl->part[1] = pre0; ctl->part[2] = u0; }
-  }
-  __syncthreads();
-  const long long total = ctl->part[0];
-  const long long g0 = total * cta / p.G, g1 = total * (cta + 1) / p.G;
-  if (g0 >= g1 || ctl->abort_flag) return;  // uniform: nothing to do, or the launch already failed
-  if (warp == 1) {
+    // Tile count of every unit: the total, and whether all units are equally long.  If they are,
+    // the grid is trimmed (by at most a fifth) to a CTA count that divides, or is divided by, the
+    // unit count: every CTA then works inside one unit, or on whole units, and no CTA pays for a
+    // change of unit that its neighbours do not have.
+    long long total = 0;
+    int mn = 0x7fffffff, mx = 0, live = 0;
+    for (int u = lane; u < n_units; u += 32) {
+      const int nt = unit_tiles<DU_BN>(p, u);
+      total += nt;
+      mn = min(mn, nt);
+      mx = max(mx, nt);
+      live += nt > 0;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      total += __shfl_xor_sync(0xffffffffu, total, o);
+      live += __shfl_xor_sync(0xffffffffu, live, o);
+      mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    int geff = p.G, lead = min(DU_SWITCH_TILES + (p.rb * GROUP) / 4, 3 * DU_SWITCH_TILES);
+    if (mn == mx && mx > 0) {
+      if (n_units <= p.G) {
+        const int k = p.G / n_units;
+        if (k * n_units * 5 >= p.G * 4) { geff = k * n_units; lead = 0; }
+      } else {
+        for (int d = p.G; d * 5 >= p.G * 4; --d)
+          if (n_units % d == 0) { geff = d; lead = 0; break; }
+      }
+    }
+    // Otherwise a CTA whose slice runs over a unit boundary loses several tiles of time there (the
+    // pipeline drains: last P V, read-out of O, new Q tile; 4 tiles measured with 6 rows, 9 with 24).  The flat list charges for
+    // it: every unit is preceded by `lead` entries that stand for no tile, so such a CTA receives
+    // that many tiles less.
+    total += (long long)lead * live;
+    int u0 = n_units; long long pre0 = 0;
+    if (cta < geff) warp_find_unit<DU_BN>(p, n_units, lane, total * cta / geff, u0, pre0, lead);
+    if (lane == 0) { ctl->part[0] = total; ctl->part[1] = pre0; ctl->part[2] = u0; ctl->part[3] = geff; ctl->part[4] = lead; }
+  } else if (warp == 1) {  // meanwhile: tensor memory
     tmem_alloc(&ctl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -108,7 +142,28 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
+  const long long total = ctl->part[0];
+  const int G = (int)ctl->part[3], LEAD = (int)ctl->part[4];
+  const long long g0 = cta < G ? total * cta / G : 0, g1 = cta < G ? total * (cta + 1) / G : 0;
+  if (g0 >= g1 || ctl->abort_flag) {  // uniform: nothing to do, or the launch already failed
+    if (warp == 1) tmem_dealloc(tmem, 512);
+    return;
+  }
   if (tid == 0) QWB_TL(30, 2);
+  // Advance (u, pre) to the next unit that has tiles inside this CTA's slice [g0, g1) of the flat
+  // list; t0 / t1 bound those tiles.  The first LEAD entries of a unit stand for no tile.
+  auto find_live = [&](int &u, long long &pre, int &nt, int &t0, int &t1) -> bool {
+    while (u < n_units && pre < g1) {
+      nt = unit_tiles<DU_BN>(p, u);
+      const int vt = nt > 0 ? nt + LEAD : 0;
+      t0 = max((int)(max(g0, pre) - pre) - LEAD, 0);
+      t1 = max((int)(min(g1, pre + vt) - pre) - LEAD, 0);
+      if (t0 < t1) return true;
+      pre += vt;
+      ++u;
+    }
+    return false;
+  };
   volatile int *abort_flag = &ctl->abort_flag;
   auto fail = [&](int code) {
     if (!*abort_flag && p.status) *p.status = code;
@@ -137,10 +192,9 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       auto advance = [&]() {
         if (++sl == DU_NSLOT) { sl = 0; ph ^= 1; wrapped = true; }
       };
-      while (pre < g1 && u < n_units && ok) {
+      int nt, t0, t1;
+      while (ok && find_live(u, pre, nt, t0, t1)) {
         const UnitInfo ui = unit_info(p, u);
-        const int nt = (ui.len + DU_BN - 1) / DU_BN;
-        const int t0 = (int)(max(g0, pre) - pre), t1 = (int)(min(g1, pre + nt) - pre);
         const long long row0 = p.cache_row ? p.cache_row[ui.s] : 0;
         for (int j = t0; j <= t1 && ok; ++j) {
           if (j < t1) {
@@ -164,15 +218,15 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
             }
           }
         }
-        pre += nt;
+        pre += nt + LEAD;
         ++u;
       }
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ==============================================
-    // The whole warp walks the tile sequence (so that it can clear ragged V rows together); the
-    // elected lane issues.  J counts tiles over all segments of this CTA: S / P buffer J & 1,
+    // One elected thread walks the tile sequence and issues everything.  J counts tiles over all segments of this CTA: S / P buffer J & 1,
     // barrier phase J >> 1.
+    if (elect_one()) {
     const uint32_t idesc_qk = make_idesc(128, 128, 1, 1, 0, 0);
     const uint32_t idesc_pv = make_idesc(128, 256, 1, 1, 0, 1);
     const uint64_t qdesc0 = smem_desc(smem_u32(q_smem), 16, 1024);
@@ -186,9 +240,9 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     int J = 0, seg = 0;
     bool ok = true;
     auto wait_all = [&](uint64_t *bar, uint32_t parity, int code) {
-      const bool got = __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag));
+      const bool got = wait_or_abort(bar, parity, abort_flag);
       if (!got) {
-        if (lane == 0) fail(code);
+        fail(code);
         ok = false;
       }
       return got;
@@ -196,10 +250,8 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     auto advance = [&]() {
       if (++sl == DU_NSLOT) { sl = 0; ph ^= 1; }
     };
-    while (pre < g1 && u < n_units && ok) {
-      const UnitInfo ui = unit_info(p, u);
-      const int nt = (ui.len + DU_BN - 1) / DU_BN;
-      const int t0 = (int)(max(g0, pre) - pre), t1 = (int)(min(g1, pre + nt) - pre);
+    int nt, t0, t1;
+    while (ok && find_live(u, pre, nt, t0, t1)) {
       if (!wait_all(&ctl->q_ready, seg & 1, DEV_ERR_MMA_WAIT)) break;
       tc_fence_after();
       for (int j = t0; j <= t1 && ok; ++j) {
@@ -207,11 +259,11 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         if (j < t1) {
           // ---- S[Jt & 1] = Q K_j^T ----
           const uint32_t d_s = tmem + ((Jt & 1) ? TMEM_S1 : TMEM_S0);
-          if (lane == 0) QWB_TL(0, Jt);
+          QWB_TL(0, Jt); QWB_TL(31, Jt);
           for (int c = 0; c < 4 && ok; ++c) {
             if (!wait_all(&ctl->slot_full[sl], ph, DEV_ERR_MMA_WAIT)) break;
             tc_fence_after();
-            if (elect_one()) {
+            {
               const uint64_t kd = kdesc0 + (uint64_t)(sl * (DU_SLOT >> 4));
               const uint64_t qd = qdesc0 + (uint64_t)(c * qsub16);
 #pragma unroll
@@ -224,38 +276,23 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
               umma_commit(&ctl->slot_empty[sl]);
               if (c == 3) umma_commit(&ctl->s_full[Jt & 1]);
             }
-            __syncwarp();
             advance();
           }
         }
         if (j > t0 && ok) {
-          if (lane == 0) QWB_TL(1, Jt);
+          QWB_TL(1, Jt);
           // ---- O (+)= P_{j-1} V_{j-1} ----
           const int jj = j - 1, Jp = Jt - 1;
           if (!wait_all(&ctl->p_full[Jp & 1], (Jp >> 1) & 1, DEV_ERR_SOFTMAX_WAIT)) break;
           // the first P V of a segment overwrites O: the previous segment must have read it out
           if (jj == t0 && seg > 0 && !wait_all(&ctl->o_free, (seg - 1) & 1, DEV_ERR_SOFTMAX_WAIT)) break;
           tc_fence_after();
-          if (lane == 0) QWB_TL(2, Jp);
+          QWB_TL(2, Jp);
           const uint32_t a_p = tmem + ((Jp & 1) ? TMEM_S1 : TMEM_S0);
           for (int g = 0; g < 4 && ok; ++g) {
             if (!wait_all(&ctl->slot_full[sl], ph, DEV_ERR_MMA_WAIT)) break;
-            // keys past the end of the unit may hold anything in V; P is zero there but 0 * NaN
-            // is NaN, so clear those rows before the tensor core reads them
-            const int key_lo = jj * DU_BN + g * 32;
-            if (key_lo + 32 > ui.len) {
-              const int valid = max(0, ui.len - key_lo);
-              for (int idx = lane; idx < 32 * 32; idx += 32) {
-                const int kr = idx >> 5, c16 = idx & 31;
-                if (kr >= valid)
-                  *reinterpret_cast<uint4 *>(ring + sl * DU_SLOT + (c16 >> 3) * 4096 + kr * 128 + (((c16 & 7) ^ (kr & 7)) << 4)) =
-                      make_uint4(0, 0, 0, 0);
-              }
-              fence_proxy_async();
-              __syncwarp();
-            }
             tc_fence_after();
-            if (elect_one()) {
+            {
               const uint64_t vd = vdesc0 + (uint64_t)(sl * (DU_SLOT >> 4));
               const uint32_t first = (uint32_t)(jj != t0) | (uint32_t)g;
 #pragma unroll
@@ -266,16 +303,16 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
               umma_commit(&ctl->slot_empty[sl]);
               if (g == 3) umma_commit(&ctl->o_done[Jp & 1]);
             }
-            __syncwarp();
             advance();
           }
-          if (lane == 0) QWB_TL(3, Jp);
+          QWB_TL(3, Jp);
         }
       }
       J += t1 - t0;
       ++seg;
-      pre += nt;
+      pre += nt + LEAD;
       ++u;
+    }
     }
   } else {
     // ============ softmax / correction / epilogue: thread = (row, 32-key column group) ============
@@ -295,16 +332,11 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         ++o_seen;
       }
     };
-    while (pre < g1 && u < n_units) {
-      const UnitInfo ui = unit_info(p, u);
-      const int nt = (ui.len + DU_BN - 1) / DU_BN;
-      const int t0 = (int)(max(g0, pre) - pre), t1 = (int)(min(g1, pre + nt) - pre);
+    // ---- stage Q of one unit: rows (token b, head hh) -> 6 b + hh, zero padding above R ----
+    // The rotary channels are rotated on the way (angle reduced in double) and split into a bf16
+    // value and its bf16 remainder.
+    auto stage_q = [&](const UnitInfo &ui) {
       const int R = ui.ntok * GROUP;
-      const bool whole = (t0 == 0 && t1 == nt);
-      const bool warp_live = (warp & 3) * 32 < R;         // this warp holds at least one real row
-
-      if (tid == 64) QWB_TL(30, 3 + 6 * segx);
-      // ---- stage Q for this unit: rows (token b, head hh) -> 6 b + hh, zero padding above R ----
       for (int idx = st_tid; idx < p.q_rows_pad * 32; idx += DU_SM_THREADS) {
         const int r = idx >> 5, c16 = idx & 31;           // 8 channels c16*8 .. +7
         if (p.do_rope && c16 < 8) continue;               // rotary channels are written pair-wise below
@@ -323,12 +355,12 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           if (r < R) {
             const size_t trow = (size_t)ui.s * p.n_new + ui.tok0 + r / GROUP;
             const uint16_t *src = reinterpret_cast<const uint16_t *>(p.q) + (trow * p.q_heads + (size_t)ui.kvh * GROUP + r % GROUP) * HEAD_DIM;
-            const double x = bf16_bits_to_f32(src[i]), y = bf16_bits_to_f32(src[i + ROT_PAIRS]);
+            const float x = bf16_bits_to_f32(src[i]), y = bf16_bits_to_f32(src[i + ROT_PAIRS]);
             const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.pos + ui.tok0 + r / GROUP;
-            double c, sn;
-            rope_sincos_exact(pz, p.rope.inv_freq[i], c, sn);
-            xr = (float)(x * c - y * sn);
-            yr = (float)(x * sn + y * c);
+            float c, sn;
+            rope_sincos_reduced(pz, p.rope.inv_freq[i], c, sn);
+            xr = x * c - y * sn;
+            yr = x * sn + y * c;
           }
           const uint16_t xh = f32_to_bf16_bits(xr), yh = f32_to_bf16_bits(yr);
           *reinterpret_cast<uint16_t *>(q_smem + q_tile_off(r, i, QSUB)) = xh;
@@ -340,7 +372,24 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       }
       fence_proxy_async();
       mbar_arrive(&ctl->q_ready);
-      if (tid == 64) QWB_TL(30, 4 + 6 * segx);
+    };
+    // units cut across CTAs: their merge is settled after this CTA's last tile
+    int pend_u[2] = {0, 0}, pend_nt[2] = {0, 0}, n_pend = 0;
+    long long pend_pre[2] = {0, 0};
+    if (tid == 64) QWB_TL(30, 3);
+    int nt, t0, t1;
+    bool have = find_live(u, pre, nt, t0, t1);
+    if (have) stage_q(unit_info(p, u));
+    if (tid == 64) QWB_TL(30, 4);
+    while (have) {
+      const UnitInfo ui = unit_info(p, u);
+      // the unit this CTA works on next, if any: its Q tile is staged ahead of time (below)
+      int u_next = u + 1, nt_next, t0_next, t1_next;
+      long long pre_next = pre + nt + LEAD;
+      const bool have_next = find_live(u_next, pre_next, nt_next, t0_next, t1_next);
+      const int R = ui.ntok * GROUP;
+      const bool whole = (t0 == 0 && t1 == nt);
+      const bool warp_live = (warp & 3) * 32 < R;         // this warp holds at least one real row
 
       // keys visible to this row; padding rows see none
       const int lim = row < R ? (p.no_causal ? ui.pos : ui.pos + ui.tok0 + row / GROUP + 1) : 0;
@@ -419,9 +468,33 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           tmem_st16(t_s + 64 + wg * 16, lo);
           tmem_wait_st();
         }
+        // Keys past the end of the unit may hold anything in V; P is zero there but 0 * NaN is NaN,
+        // so those rows are cleared before the tensor core reads them.  The ragged tile is the
+        // unit's last, hence the last of its segment: its V slots are the four that follow the
+        // 8 Jt + 4 slots consumed before them.
+        if (j * DU_BN + DU_BN > ui.len) {
+          for (int g = 0; g < 4; ++g) {
+            const int key_lo = j * DU_BN + g * 32;
+            if (key_lo + 32 <= ui.len) continue;
+            const uint32_t itv = 8u * (uint32_t)Jt + 4u + (uint32_t)g;
+            const int sl = (int)(itv % (uint32_t)DU_NSLOT);
+            if (ok) ok = wait_or_abort(&ctl->slot_full[sl], (itv / (uint32_t)DU_NSLOT) & 1u, abort_flag);
+            const int valid = max(0, ui.len - key_lo);
+            for (int idx = st_tid; idx < 32 * 32; idx += DU_SM_THREADS) {
+              const int kr = idx >> 5, c16 = idx & 31;
+              if (kr >= valid)
+                *reinterpret_cast<uint4 *>(ring + sl * DU_SLOT + (c16 >> 3) * 4096 + kr * 128 + (((c16 & 7) ^ (kr & 7)) << 4)) =
+                    make_uint4(0, 0, 0, 0);
+            }
+          }
+          fence_proxy_async();
+        }
         tc_fence_before();
         mbar_arrive(&ctl->p_full[Jt & 1]);
         if (tid == 64) QWB_TL(8, Jt);
+        // Last tile of the segment: every Q K^T of this unit has completed (s_full above), so the Q
+        // tile is free -- stage the next unit's rows while the tensor core runs this tile's P V.
+        if (j == t1 - 1 && have_next) stage_q(unit_info(p, u_next));
         if (j > t0) wait_pv_done(Jt - 1);
         if (tid == 64) QWB_TL(9, Jt);
       }
@@ -488,26 +561,99 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         if (lane == 0) fail(DEV_ERR_SOFTMAX_WAIT);
         break;
       }
-      // ---- a unit cut across CTAs is merged by whichever of them arrives last ----
-      if (!whole) {
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
-        if (st_tid == 0) ctl->ticket = atomicAdd(&p.cnt[u], 1);
-        asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
-        const int c_first = cta_of_tile(pre, total, p.G), c_last = cta_of_tile(pre + nt - 1, total, p.G);
-        int nparts = 0;
-        for (int c = c_first; c <= c_last; ++c) nparts += (total * c / p.G != total * (c + 1) / p.G) ? 1 : 0;
-        if (ctl->ticket == nparts - 1) {
-          __threadfence();
-          for (int r = warp - 2; r < R; r += DU_NWG * 4) merge_unit_row<TOut>(p, u, ui, r, c_first, c_last, total, lane);
-          if (st_tid == 0) p.cnt[u] = 0;
-        }
+      if (!whole) {  // at most the first and the last segment of a CTA
+        pend_u[n_pend] = u; pend_nt[n_pend] = nt; pend_pre[n_pend] = pre;
+        ++n_pend;
       }
       if (tid == 64) QWB_TL(30, 7 + 6 * segx);
       ++segx;
       J += t1 - t0;
-      pre += nt;
-      ++u;
+      have = have_next;
+      u = u_next; pre = pre_next; nt = nt_next; t0 = t0_next; t1 = t1_next;
+    }
+    // ---- units cut across CTAs are merged by whichever of their CTAs arrives last ----
+    if (tid == 64) QWB_TL(30, 50);
+    if (n_pend > 0) {  // n_pend is the same in all softmax threads
+      // which CTAs of c_first .. c_last hold a part (one thread per CTA: the test is two 64-bit divisions)
+      for (int k = 0; k < n_pend; ++k) {
+        const int c_first = cta_of_tile(pend_pre[k] + LEAD, total, G), c_last = cta_of_tile(pend_pre[k] + LEAD + pend_nt[k] - 1, total, G);
+        for (int i = st_tid; i <= c_last - c_first && i < DU_MAX_PARTS; i += DU_SM_THREADS)
+          ctl->merge_live[k][i] = (total * (c_first + i) / G != total * (c_first + i + 1) / G) ? 1 : 0;
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+      if (tid == 64) QWB_TL(30, 51);
+      if (st_tid == 0) {  // one thread decides, so that a failure flagged meanwhile cannot split the group
+        const int go = *abort_flag ? 0 : 1;
+        for (int k = 0; k < n_pend && go; ++k) {
+          const int c_first = cta_of_tile(pend_pre[k] + LEAD, total, G), c_last = cta_of_tile(pend_pre[k] + LEAD + pend_nt[k] - 1, total, G);
+          int nparts = 0;
+          for (int i = 0; i <= c_last - c_first; ++i)
+            nparts += i < DU_MAX_PARTS ? ctl->merge_live[k][i] : ((total * (c_first + i) / G != total * (c_first + i + 1) / G) ? 1 : 0);
+          ctl->merge_parts[k] = nparts;
+          ctl->ticket[k] = atomicAdd(&p.cnt[pend_u[k]], 1);
+        }
+        ctl->merge_go = go;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+      if (tid == 64) QWB_TL(30, 52);
+      for (int k = 0; k < n_pend && ctl->merge_go; ++k) {
+        if (tid == 64) { QWB_TL(30, 53 + 3 * k); QWB_TLV(29, k, ctl->merge_parts[k] * 1000 + ctl->ticket[k]); }
+        if (ctl->ticket[k] == ctl->merge_parts[k] - 1) {
+          __threadfence();
+          if (tid == 64) QWB_TL(30, 54 + 3 * k);
+          const int c_first = cta_of_tile(pend_pre[k] + LEAD, total, G), c_last = cta_of_tile(pend_pre[k] + LEAD + pend_nt[k] - 1, total, G);
+          const UnitInfo ui = unit_info(p, pend_u[k]);
+          const int R = ui.ntok * GROUP, span = c_last - c_first + 1, P = ctl->merge_parts[k];
+          constexpr int ROW_BYTES = PART_STRIDE * 4, ROW_CHUNKS = ROW_BYTES / 16;
+          const int cap_rows = (DU_SMEM_TOTAL - (int)sizeof(DecCtl)) / ROW_BYTES;  // part rows that fit in shared memory
+          if (DU_STAGED_MERGE && span <= DU_MAX_PARTS && P <= cap_rows) {
+            // All parts of a group of rows are fetched into the (now idle) Q / ring area with 16-byte
+            // asynchronous copies, every one of them in flight at once: one memory round trip per
+            // group instead of one per four parts.  Then a warp folds each row, in CTA order.
+            const int rows_per = min(R, cap_rows / P);
+            for (int r0 = 0; r0 < R; r0 += rows_per) {
+              const int nr = min(rows_per, R - r0);
+              for (int idx = st_tid; idx < nr * span * ROW_CHUNKS; idx += DU_SM_THREADS) {
+                const int chunk = idx % ROW_CHUNKS, rp = idx / ROW_CHUNKS, i = rp % span, rr = rp / span;
+                if (!ctl->merge_live[k][i]) continue;
+                const float *src = p.ws + ((size_t)(c_first + i + pend_u[k]) * (p.rb * GROUP) + r0 + rr) * PART_STRIDE + chunk * 4;
+                cp_async16(smem + ((size_t)(rr * span + i) * ROW_BYTES + chunk * 16), src);
+              }
+              cp_async_wait_all();
+              asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+              for (int rr = warp - 2; rr < nr; rr += DU_NWG * 4) {
+                float mg = -INFINITY, lg = 0.f;
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int i = 0; i < span; ++i) {
+                  if (!ctl->merge_live[k][i]) continue;
+                  const float *src = reinterpret_cast<const float *>(smem + (size_t)(rr * span + i) * ROW_BYTES);
+                  const float mv = src[256], lv = src[257];
+                  if (!(lv > 0.f)) continue;
+                  const float4 av = *reinterpret_cast<const float4 *>(src + lane * 8);
+                  const float4 bv = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
+                  const float m_new = fmaxf(mg, mv);
+                  const float f_old = fast_exp2(mg - m_new), f = fast_exp2(mv - m_new);  // mg = -inf gives f_old = 0
+                  mg = m_new;
+                  lg = lg * f_old + lv * f;
+                  acc[0] = acc[0] * f_old + av.x * f; acc[1] = acc[1] * f_old + av.y * f;
+                  acc[2] = acc[2] * f_old + av.z * f; acc[3] = acc[3] * f_old + av.w * f;
+                  acc[4] = acc[4] * f_old + bv.x * f; acc[5] = acc[5] * f_old + bv.y * f;
+                  acc[6] = acc[6] * f_old + bv.z * f; acc[7] = acc[7] * f_old + bv.w * f;
+                }
+                merge_finish<TOut>(p, ui, r0 + rr, lane, mg, lg, acc);
+              }
+              asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+            }
+          } else {
+            for (int r = warp - 2; r < R; r += DU_NWG * 4)
+              merge_unit_row<TOut>(p, pend_u[k], ui, r, c_first, c_last, total, lane, G,
+                                   span <= DU_MAX_PARTS ? ctl->merge_live[k] : nullptr);
+          }
+          if (st_tid == 0) p.cnt[pend_u[k]] = 0;
+          if (tid == 64) QWB_TL(30, 55 + 3 * k);
+        }
+      }
     }
   }
 
@@ -515,6 +661,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   if (tid == 64) QWB_TL(30, 40);
   tc_fence_before();
   __syncthreads();
+  if (tid == 0) QWB_TLB(1);
   if (warp == 1) {
     if (*abort_flag) {
       const uint64_t t0 = global_timer_ns();
