@@ -6,7 +6,8 @@
 Prints ONE JSON line.  The headline workload is BASELINE.json's decode configuration (16
 sequences x 1 query token against 8192 cached tokens, 24/4 heads, head_dim 256, bf16); the same
 line carries, under "prefill", the other half of the metric: causal prefill attention at 8K
-context on the tcgen05 kernel.  A step is one fused mixer call over the whole batch: rope(q, k),
+context on the tcgen05 kernel, and under "verify" the MTP-verify batch (8 ragged sequences x 4
+query tokens) on the tcgen05 split-KV kernel.  A step is one fused mixer call over the whole batch: rope(q, k),
 KV append, attention, sigmoid gate.
 """
 import argparse
@@ -249,7 +250,8 @@ def hbm_line(name, r, world, peaks):
                      "traffic": 543.4e6 if (name == "decode" and world == 1) else None,
                      "traffic_source": "ncu dram read+write bytes per launch, profiles/splitkv_decode_config2.txt",
                      "algorithmic_bytes": w["kv_bytes"], "peak_kind": kind,
-                     "kernel": "splitkv_kernel", "kernel_ms": round(r["kernel_ms"], 5)},
+                     "kernel": "splitkv_kernel" if name == "decode" else "splitkv_umma_kernel",
+                     "kernel_ms": round(r["kernel_ms"], 5)},
         "e2e": {"value": round(r["kv_bytes_all"] / (r["e2e_ms_per_step"] * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
         "gpu_launches": r["launches"],
@@ -326,6 +328,11 @@ def run_ours(args, rank, local_rank, world):
                 fast = tensor_line("prefill8k", rf, world, peaks, "single bf16 (rel-L2 ~1.4e-3)")
                 line["prefill"]["fast_p"] = {"value": fast["value"], "unit": "TFLOP/s", "ms_per_step": fast["ms_per_step"],
                                              "roofline_frac": fast["roofline"]["frac"]}
+            rv = measure("verify", args, rank, world, with_e2e=False)
+            if rank == 0:
+                v = hbm_line("verify", dict(rv, e2e_ms_per_step=rv["ms_per_step"]), world, peaks)
+                line["verify"] = {"value": v["value"], "unit": v["unit"], "ms_per_step": v["ms_per_step"],
+                                  "workload": v["config"]["workload"], "roofline": v["roofline"]}
     else:
         r = measure(args.workload, args, rank, world, flags_extra=api.F_FAST_P if args.fast_p else 0)
         line = tensor_line(args.workload, r, world, peaks,
@@ -348,7 +355,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS))
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--fast-p", action="store_true", help="prefill workloads: single-bf16 P operand")
-    ap.add_argument("--no-prefill", action="store_true", help="decode workload: skip the prefill8k sub-measurement")
+    ap.add_argument("--no-prefill", action="store_true", help="decode workload: skip the prefill8k and verify sub-measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()

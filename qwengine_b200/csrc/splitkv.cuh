@@ -90,6 +90,42 @@ __device__ __forceinline__ long long warp_total_tiles(const SplitKVParams &p, in
   for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
   return t;
 }
+// Warp-cooperative: total tiles, units that have any, and the number of CTAs to spread them over.
+// When all units are equally long the grid is trimmed (by at most a fifth) to a count that divides,
+// or is divided by, the unit count: every CTA then stays inside one unit, or takes whole units, and
+// none pays for a change of unit that its neighbours do not have (`aligned`).
+template <int TK = SK_TK>
+__device__ __forceinline__ void warp_partition(const SplitKVParams &p, int n_units, int lane, long long &total, int &live,
+                                               int &geff, bool &aligned) {
+  total = 0;
+  live = 0;
+  int mn = 0x7fffffff, mx = 0;
+  for (int u = lane; u < n_units; u += 32) {
+    const int nt = unit_tiles<TK>(p, u);
+    total += nt;
+    mn = min(mn, nt);
+    mx = max(mx, nt);
+    live += nt > 0;
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    total += __shfl_xor_sync(0xffffffffu, total, o);
+    live += __shfl_xor_sync(0xffffffffu, live, o);
+    mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  geff = p.G;
+  aligned = false;
+  if (mn == mx && mx > 0) {
+    if (n_units <= p.G) {
+      const int k = p.G / n_units;
+      if (k * n_units * 5 >= p.G * 4) { geff = k * n_units; aligned = true; }
+    } else {
+      for (int d = p.G; d * 5 >= p.G * 4; --d)
+        if (n_units % d == 0) { geff = d; aligned = true; break; }
+    }
+  }
+}
 // Warp-cooperative: the unit containing flat tile g and the flat index of that unit's tile 0.
 template <int TK = SK_TK>
 __device__ __forceinline__ void warp_find_unit(const SplitKVParams &p, int n_units, int lane, long long g,
@@ -272,19 +308,20 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     prefetch_tensormap(&mapV);
   }
   if (warp == 0) {
-    const long long total = warp_total_tiles(p, n_units, lane);
-    const long long g0 = total * cta / p.G;
-    int u0; long long pre0;
-    warp_find_unit(p, n_units, lane, g0, u0, pre0);
-    if (lane == 0) { seg[0] = total; seg[1] = pre0; seg[2] = u0; }
+    long long total; int live, geff; bool aligned;
+    warp_partition(p, n_units, lane, total, live, geff, aligned);
+    int u0 = n_units; long long pre0 = 0;
+    if (cta < geff) warp_find_unit(p, n_units, lane, total * cta / geff, u0, pre0);
+    if (lane == 0) { seg[0] = total; seg[1] = pre0; seg[2] = (long long)u0 | ((long long)geff << 32); }
   }
   __syncthreads();
   const long long total = seg[0];
-  const long long g0 = total * cta / p.G, g1 = total * (cta + 1) / p.G;
+  const int G = (int)(seg[2] >> 32);                  // CTAs in use (the rest of the grid leaves here)
+  const long long g0 = cta < G ? total * cta / G : 0, g1 = cta < G ? total * (cta + 1) / G : 0;
   if (g0 >= g1) return;  // uniform for the whole CTA
 
   // ---------------- producer: one lane streams the tiles of every segment, in order -----------
-  int pu = (int)seg[2];                              // unit of the next tile to load
+  int pu = (int)(seg[2] & 0xffffffffll);                              // unit of the next tile to load
   long long ppre = seg[1];                           // flat index of that unit's tile 0
   int pt = (int)(max(g0, ppre) - ppre);              // next tile within the unit
   uint32_t pit = 0;                                  // tiles issued so far
@@ -340,7 +377,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   const int qd = lane >> 2, ql = lane & 3;  // row-in-8 and column pair of the mma fragments
   bool ok = true;
   uint32_t it = 0;
-  int u = (int)seg[2];
+  int u = (int)(seg[2] & 0xffffffffll);
   long long pre = seg[1];
   const uint32_t qhi_s = smem_u32(qregion);
   // Per-lane ldmatrix addresses.  The swizzle XORs the 16-byte column (d / 8) & 7 with row & 7,
@@ -678,12 +715,12 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       consumer_sync(NCT);
       if (tid == 0) *ticket = atomicAdd(&p.cnt[u], 1);
       consumer_sync(NCT);
-      const int c_first = cta_of_tile(pre, total, p.G), c_last = cta_of_tile(pre + nt_unit - 1, total, p.G);
+      const int c_first = cta_of_tile(pre, total, G), c_last = cta_of_tile(pre + nt_unit - 1, total, G);
       int nparts = 0;
-      for (int c = c_first; c <= c_last; ++c) nparts += (total * c / p.G != total * (c + 1) / p.G) ? 1 : 0;
+      for (int c = c_first; c <= c_last; ++c) nparts += (total * c / G != total * (c + 1) / G) ? 1 : 0;
       if (*ticket == nparts - 1) {
         __threadfence();
-        for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, p.G);
+        for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, G);
         if (tid == 0) p.cnt[u] = 0;  // leave the counter clean for a caller that does not reset it
       }
     }
@@ -698,21 +735,23 @@ template <typename TOut>
 __global__ void __launch_bounds__(256) splitkv_merge_kernel(const __grid_constant__ SplitKVParams p) {
   const int u = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
-  __shared__ long long sh[2];
+  __shared__ long long sh[3];
   if (warp == 0) {
-    const long long total = warp_total_tiles(p, n_units, lane);
+    long long total; int live, geff; bool aligned;
+    warp_partition(p, n_units, lane, total, live, geff, aligned);
     const long long pre = warp_unit_prefix(p, u, lane);
-    if (lane == 0) { sh[0] = total; sh[1] = pre; }
+    if (lane == 0) { sh[0] = total; sh[1] = pre; sh[2] = geff; }
   }
   __syncthreads();
   const long long total = sh[0], pre = sh[1];
+  const int G = (int)sh[2];
   const UnitInfo ui = unit_info(p, u);
   const int nt = (ui.len + SK_TK - 1) / SK_TK;
   if (nt == 0 || total == 0) return;
-  const int c_first = cta_of_tile(pre, total, p.G), c_last = cta_of_tile(pre + nt - 1, total, p.G);
+  const int c_first = cta_of_tile(pre, total, G), c_last = cta_of_tile(pre + nt - 1, total, G);
   if (c_first == c_last) return;  // the main kernel already wrote this unit
   const int R = ui.ntok * GROUP;
-  for (int row = warp; row < R; row += 8) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, p.G);
+  for (int row = warp; row < R; row += 8) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, G);
 }
 
 // Merge n_parts partial sets [n_parts][n][PART_STRIDE] (n = rows * q_heads) in index order, then

@@ -96,40 +96,13 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     prefetch_tensormap(&mapV);
   }
   if (warp == 2) {
-    // Tile count of every unit: the total, and whether all units are equally long.  If they are,
-    // the grid is trimmed (by at most a fifth) to a CTA count that divides, or is divided by, the
-    // unit count: every CTA then works inside one unit, or on whole units, and no CTA pays for a
-    // change of unit that its neighbours do not have.
-    long long total = 0;
-    int mn = 0x7fffffff, mx = 0, live = 0;
-    for (int u = lane; u < n_units; u += 32) {
-      const int nt = unit_tiles<DU_BN>(p, u);
-      total += nt;
-      mn = min(mn, nt);
-      mx = max(mx, nt);
-      live += nt > 0;
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      total += __shfl_xor_sync(0xffffffffu, total, o);
-      live += __shfl_xor_sync(0xffffffffu, live, o);
-      mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    }
-    int geff = p.G, lead = min(DU_SWITCH_TILES + (p.rb * GROUP) / 4, 3 * DU_SWITCH_TILES);
-    if (mn == mx && mx > 0) {
-      if (n_units <= p.G) {
-        const int k = p.G / n_units;
-        if (k * n_units * 5 >= p.G * 4) { geff = k * n_units; lead = 0; }
-      } else {
-        for (int d = p.G; d * 5 >= p.G * 4; --d)
-          if (n_units % d == 0) { geff = d; lead = 0; break; }
-      }
-    }
-    // Otherwise a CTA whose slice runs over a unit boundary loses several tiles of time there (the
-    // pipeline drains: last P V, read-out of O, new Q tile; 4 tiles measured with 6 rows, 9 with 24).  The flat list charges for
-    // it: every unit is preceded by `lead` entries that stand for no tile, so such a CTA receives
-    // that many tiles less.
+    long long total; int live, geff; bool aligned;
+    warp_partition<DU_BN>(p, n_units, lane, total, live, geff, aligned);
+    const int lead = aligned ? 0 : min(DU_SWITCH_TILES + (p.rb * GROUP) / 4, 3 * DU_SWITCH_TILES);
+    // Where the grid could not be aligned with the units, a CTA whose slice runs over a unit
+    // boundary loses several tiles of time there (the pipeline drains: last P V, read-out of O, new
+    // Q tile; 4 tiles measured with 6 rows, 9 with 24).  The flat list charges for it: every unit is
+    // preceded by `lead` entries that stand for no tile, so such a CTA receives that many tiles less.
     total += (long long)lead * live;
     int u0 = n_units; long long pre0 = 0;
     if (cta < geff) warp_find_unit<DU_BN>(p, n_units, lane, total * cta / geff, u0, pre0, lead);
