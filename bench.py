@@ -247,8 +247,9 @@ def hbm_line(name, r, world, peaks):
                    "l2_policy": "inputs larger than L2: %.0f MB of KV per GPU per step vs 126 MB L2" % (w["kv_bytes"] / 1e6)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
                      "frac": round(achieved / hbm_peak, 4),
-                     "traffic": 543.4e6 if (name == "decode" and world == 1) else None,
-                     "traffic_source": "ncu dram read+write bytes per launch, profiles/splitkv_decode_config2.txt",
+                     "traffic": ({"decode": 546.2e6, "verify": 690.8e6}[name] if world == 1 else None),
+                     "traffic_source": "ncu dram read+write bytes per launch, profiles/%s.txt"
+                                       % ("splitkv_decode_config2" if name == "decode" else "splitkv_umma_verify"),
                      "algorithmic_bytes": w["kv_bytes"], "peak_kind": kind,
                      "kernel": "splitkv_kernel" if name == "decode" else "splitkv_umma_kernel",
                      "kernel_ms": round(r["kernel_ms"], 5)},
@@ -272,7 +273,7 @@ def tensor_line(name, r, world, peaks, mode):
                                 % (3 * w["q"].numel() * 2 / 1e6)},
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": tc_peak, "unit": "TFLOP/s",
                      "frac": round(achieved / tc_peak, 4),
-                     "traffic": 316.5e6 if (name == "prefill8k" and world == 1) else None,
+                     "traffic": 319.5e6 if (name == "prefill8k" and world == 1) else None,
                      "traffic_source": "ncu dram read+write bytes per launch, profiles/prefill_umma_pair_8k.txt",
                      "algorithmic_flops": w["flops"], "peak_kind": kind,
                      "kernel": "prefill_umma_pair_kernel", "kernel_ms": round(r["kernel_ms"], 5),
