@@ -115,11 +115,12 @@ def run_reference(args, rank, local_rank, world):
         value = w["flops"] / (ms * 1e-3) / 1e12 if ms else None
         metric, unit = "prefill_attn_TFLOPs", "TFLOP/s"
     line = {
-        "impl": "reference", "metric": metric, "value": round(value, 4) if value else None, "unit": unit, "n_gpus": 1,
+        "impl": "reference", "metric": metric, "value": round(value, 4) if value else None, "unit": unit, "n_gpus": int(getattr(args, "gpus", 1) or 1), "ranks_used": 1,
         "steps": steps, "warmup": warm, "ms_per_step": round(ms, 5) if ms else None, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32" if kind == "reference" else "f64",
         "data": "synthetic: the same seeded tensors as the B200 arm, widened to fp32",
         "config": {"workload": bench.describe(name, 1, w), "how": how,
+                   "ranks": "rank 0 alone runs one GPU's share of the weak-scaled batch; the value is per GPU",
                    "note": "algorithmic unit is the same as the B200 arm's (4096 B of bf16 K+V per cached token, "
                            "24576 FLOP per pair); the reference itself moves fp32"},
         "cpu_baseline": dict(cpu, kind="port") if cpu else {"kind": kind, "cores": cores, "sample": how, "value": round(value, 4) if value else None, "unit": unit},

@@ -18,6 +18,11 @@
  *   - sigmoid output gate .......................... src/mixers.cu:653-657
  *   - operation order rope(q), rope(k), append, attend, gate
  *     ............................ src/model.cu:228-240, src/prefill.cu:142-156
+ *   - the steps that feed the path from the fused q/k/v projection row (oracle_fused_rows):
+ *     scatter of [q|gate x heads, k, v] .............. src/elem.cu:226-237
+ *     per-head de-interleave of query and gate ....... src/mixers.cu:382-390
+ *     per-head RMSNorm with (1 + weight) on q and k .. src/mixers.cu:393-413
+ *     in the order of ................................ src/model.cu:219-226
  *
  * Differences from the reference, all deliberate:
  *   - libm pow/sincos/exp in double instead of the __powf/__sincosf/__expf fast
@@ -295,6 +300,43 @@ void oracle_combine2(const float *o1, float m1, float l1, const float *o2, float
   for (int d = 0; d < dim; ++d) o[d] = (float)(a1 * o1[d] + a2 * o2[d]);
   *m = (float)mm;
   *l = (float)(a1 * l1 + a2 * l2);
+}
+
+/* From the fused projection rows to the mixer's inputs.
+ * fused[r] = [ (q[256] | gate[256]) x q_heads | k[kv_heads*256] | v[kv_heads*256] ]  (src/model.cu:219-222).
+ * k_unpack3 (src/elem.cu:226-237) scatters the three parts, k_split_qgate (src/mixers.cu:382-390)
+ * separates query and gate per head, k_rmsnorm_head (src/mixers.cu:393-413) scales every q and k
+ * head by rsqrt(mean(x^2) + eps) * (1 + w[d]) with bf16 weights shared by all heads.  Sums in double.
+ * round_bf16 != 0 rounds q, gate, k and v to bf16 on the way out: that is where the B200 path stores
+ * them (its activations are bf16); 0 keeps the reference's fp32 values. */
+void oracle_fused_rows(const float *fused, int64_t n_rows, int q_heads, int kv_heads, int dim,
+                       const uint16_t *q_norm_w, const uint16_t *k_norm_w, double eps, int round_bf16,
+                       float *q, float *gate, float *k, float *v) {
+  const int64_t width = (int64_t)q_heads * 2 * dim + 2 * (int64_t)kv_heads * dim;
+  for (int64_t r = 0; r < n_rows; ++r) {
+    const float *row = fused + r * width;
+    const float *krow = row + (int64_t)q_heads * 2 * dim;
+    const float *vrow = krow + (int64_t)kv_heads * dim;
+    for (int h = 0; h < q_heads + kv_heads; ++h) {
+      const int is_q = h < q_heads;
+      const float *x = is_q ? row + (int64_t)h * 2 * dim : krow + (int64_t)(h - q_heads) * dim;
+      const uint16_t *w = is_q ? q_norm_w : k_norm_w;
+      float *dst = is_q ? q + (r * q_heads + h) * dim : k + (r * kv_heads + (h - q_heads)) * dim;
+      double ss = 0.0;
+      for (int d = 0; d < dim; ++d) ss += (double)x[d] * (double)x[d];
+      const double sc = 1.0 / sqrt(ss / dim + eps);
+      for (int d = 0; d < dim; ++d) {
+        const float y = (float)((double)x[d] * sc * (1.0 + (double)bf16_to_f32(w[d])));
+        dst[d] = round_bf16 ? bf16_to_f32(f32_to_bf16(y)) : y;
+      }
+      if (is_q) {
+        float *gd = gate + (r * q_heads + h) * dim;
+        for (int d = 0; d < dim; ++d) gd[d] = round_bf16 ? bf16_to_f32(f32_to_bf16(x[dim + d])) : x[dim + d];
+      }
+    }
+    for (int64_t i = 0; i < (int64_t)kv_heads * dim; ++i)
+      v[r * kv_heads * dim + i] = round_bf16 ? bf16_to_f32(f32_to_bf16(vrow[i])) : vrow[i];
+  }
 }
 
 /* Exposed so tests can check the rounding rule itself. */

@@ -34,6 +34,9 @@ def lib():
         l.oracle_gate_sigmoid_f32.restype = None
         l.oracle_gate_sigmoid_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
         l.oracle_num_threads.restype = C.c_int
+        l.oracle_fused_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                        C.c_double, C.c_int] + [C.c_void_p] * 4
+        l.oracle_fused_rows.restype = None
         l.oracle_set_threads.argtypes = [C.c_int]
         l.oracle_f32_to_bf16.restype = C.c_uint16
         l.oracle_f32_to_bf16.argtypes = [C.c_float]
@@ -87,6 +90,24 @@ def mixer(q, k_new, v_new, gate, kc, vc, pos, cache_row=None, mpos=None, rows=No
     if rc:
         raise RuntimeError("oracle_mixer failed: %d" % rc)
     return out, lse
+
+
+def fused_rows(fused, q_norm_w, k_norm_w, q_heads=24, kv_heads=4, dim=256, eps=1e-6, round_bf16=True):
+    """Fused projection rows [n_rows, q_heads*2*dim + 2*kv_heads*dim] (float32) -> (q, gate, k, v) float32
+    arrays [n_rows, heads, dim]: scatter, query/gate de-interleave and per-head RMSNorm with (1 + w);
+    q_norm_w / k_norm_w are bf16 bit patterns (uint16) of length dim."""
+    fused = np.ascontiguousarray(fused, np.float32)
+    n_rows = fused.shape[0]
+    assert fused.shape[1] == q_heads * 2 * dim + 2 * kv_heads * dim
+    qw = np.ascontiguousarray(q_norm_w, np.uint16)
+    kw = np.ascontiguousarray(k_norm_w, np.uint16)
+    q = np.empty((n_rows, q_heads, dim), np.float32)
+    gate = np.empty((n_rows, q_heads, dim), np.float32)
+    k = np.empty((n_rows, kv_heads, dim), np.float32)
+    v = np.empty((n_rows, kv_heads, dim), np.float32)
+    lib().oracle_fused_rows(_ptr(fused), n_rows, q_heads, kv_heads, dim, _ptr(qw), _ptr(kw), float(eps),
+                            int(round_bf16), _ptr(q), _ptr(gate), _ptr(k), _ptr(v))
+    return q, gate, k, v
 
 
 def rope_f32(v, pos0, theta=1e7, rot=64, mpos=None):

@@ -10,6 +10,9 @@
 //   ref_attn_decode   k_attn_decode<<<>>>   src/model.cu:236-238
 //   ref_attn_prefill  k_attn_prefill<<<>>>  src/prefill.cu:152-154
 //   ref_gate_sigmoid  k_gate_sigmoid<<<>>>  src/model.cu:239-240
+//   ref_unpack3       unpack3()              src/model.cu:221
+//   ref_split_qgate   k_split_qgate<<<>>>    src/model.cu:223-224
+//   ref_rmsnorm_head  k_rmsnorm_head<<<>>>   src/model.cu:225-226
 // All tensors are fp32, as in the reference.
 #include "src/elem.cu"
 #include "src/mixers.cu"
@@ -49,6 +52,22 @@ int ref_attn_prefill(const float *q, const float *kc, const float *vc, float *ou
 
 int ref_gate_sigmoid(float *x, const float *gate, int n, void *stream) {
   k_gate_sigmoid<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(x, gate, n);
+  return (int)cudaGetLastError();
+}
+
+int ref_unpack3(const float *fused, float *a, float *b, float *c, int na, int nb, int nc, int B, void *stream) {
+  unpack3(fused, a, b, c, na, nb, nc, B, (cudaStream_t)stream);
+  return (int)cudaGetLastError();
+}
+
+int ref_split_qgate(const float *qproj, float *q, float *gate, int rows_times_heads, int dim, void *stream) {
+  k_split_qgate<<<(rows_times_heads * dim + 255) / 256, 256, 0, (cudaStream_t)stream>>>(qproj, q, gate,
+                                                                                         rows_times_heads, dim);
+  return (int)cudaGetLastError();
+}
+
+int ref_rmsnorm_head(float *x, const uint16_t *w, int rows_times_heads, int dim, float eps, void *stream) {
+  k_rmsnorm_head<<<rows_times_heads, 256, 0, (cudaStream_t)stream>>>(x, w, dim, eps);
   return (int)cudaGetLastError();
 }
 

@@ -43,7 +43,8 @@ def test_oracle_matches_hf_golden(path):
     assert np.abs(lse - z["lse"]).max() < 2e-6
 
 
-_REF = sorted(glob.glob(os.path.join(GOLDEN, "ref_*.npz")))
+_REF = sorted(p for p in glob.glob(os.path.join(GOLDEN, "ref_*.npz")) if "ref_fused" not in p)
+_REF_FUSED = sorted(glob.glob(os.path.join(GOLDEN, "ref_fused_*.npz")))
 
 
 @pytest.mark.skipif(not _REF, reason="no reference-kernel fixtures committed yet")
@@ -63,6 +64,27 @@ def test_oracle_matches_reference_kernel_golden(path):
                      mpos=mpos, kv_heads=kvh)
     assert np.array_equal(vc[hist:], z["v_rows"])
     assert np.abs(kc[hist:] - z["k_rows"]).max() < 2e-4, "rotated K rows"
+    assert np.abs(out - z["out"]).max() < 2e-4 and rel_l2(out, z["out"]) < 1e-4
+
+
+@pytest.mark.skipif(not _REF_FUSED, reason="no fused-row fixtures committed yet")
+@pytest.mark.parametrize("path", _REF_FUSED, ids=os.path.basename)
+def test_oracle_fused_rows_match_reference_kernel_golden(path):
+    """From the fused projection row on: k_unpack3, k_split_qgate and k_rmsnorm_head as the reference's own
+    kernels ran them (src/model.cu:219-226), then the layer.  fp32 everywhere, as in the reference."""
+    z = np.load(path)
+    kvh, hist, n_new = int(z["kv_heads"]), int(z["hist"]), int(z["n_new"])
+    q, gate, k, v = O.fused_rows(z["fused"], z["q_norm_w"], z["k_norm_w"], q_heads=6 * kvh, kv_heads=kvh,
+                                 eps=float(z["eps"]), round_bf16=False)
+    assert np.array_equal(gate, z["gate"]) and np.array_equal(v.reshape(n_new, -1), z["v_rows"])
+    assert np.abs(q - z["q_norm"]).max() < 2e-5 and np.abs(k - z["k_norm"]).max() < 2e-5
+    f = O.bf16_bits_to_f32
+    kc = np.zeros((hist + n_new, kvh * 256), np.float32)
+    vc = np.zeros_like(kc)
+    kc[:hist] = f(z["kc0"]).reshape(hist, kvh * 256)
+    vc[:hist] = f(z["vc0"]).reshape(hist, kvh * 256)
+    out, _ = O.mixer(q[None], k[None], v[None], gate[None], kc, vc, [hist], kv_heads=kvh)
+    assert np.abs(kc[hist:] - z["k_rows"]).max() < 2e-4, "normalised, rotated K rows"
     assert np.abs(out - z["out"]).max() < 2e-4 and rel_l2(out, z["out"]) < 1e-4
 
 
