@@ -148,13 +148,25 @@ def build_workload(name, n_gpus, rank, seed):
     return w
 
 
-def measure(name, args, rank, world, flags_extra=0, with_e2e=True):
-    """Times `steps` fused-mixer calls on workload `name`.  Returns a dict of rank-reduced results."""
+def measure(name, args, rank, world, flags_extra=0, with_e2e=True, fused_rows=False):
+    """Times `steps` fused-mixer calls on workload `name`.  Returns a dict of rank-reduced results.
+    fused_rows: feed the call with the fused q/k/v projection rows (fp32, as the reference's GEMM emits
+    them) through qw_mixer_forward_fused instead of separate q, k, v and gate tensors."""
     from qwengine_b200 import api
     w = build_workload(name, world, rank, args.seed)
     mx = api.Mixer(w["n_seq"], w["n_new"], kv_heads=w["kv_heads"])
-    mx.bind(w["q"], w["kc"], w["vc"], w["pos"], w["out"], k_new=w["k_new"], v_new=w["v_new"], gate=w["gate"],
-            lse=w["lse"], cache_row=w["cache_row"], flags=api.F_ROPE | api.F_APPEND | api.F_GATE | flags_extra)
+    if fused_rows:
+        g = torch.Generator(device="cuda").manual_seed(args.seed + 7)
+        kvh = w["kv_heads"]
+        rows = torch.randn(w["n_seq"] * w["n_new"], 6 * kvh * 512 + 2 * kvh * 256, device="cuda", generator=g)
+        nw = [(0.2 * torch.randn(256, device="cuda", generator=g)).to(torch.bfloat16) for _ in range(2)]
+        mx.bind(w["q"], w["kc"], w["vc"], w["pos"], w["out"], gate=w["gate"], lse=w["lse"], cache_row=w["cache_row"],
+                flags=api.F_ROPE | api.F_APPEND | api.F_GATE | flags_extra, fused=True)
+        mx.forward = lambda: mx.forward_fused(rows, nw[0], nw[1])
+        with_e2e = False
+    else:
+        mx.bind(w["q"], w["kc"], w["vc"], w["pos"], w["out"], k_new=w["k_new"], v_new=w["v_new"], gate=w["gate"],
+                lse=w["lse"], cache_row=w["cache_row"], flags=api.F_ROPE | api.F_APPEND | api.F_GATE | flags_extra)
     api.profile_enable(True)
     steps = args.steps if w["n_new"] < 64 else max(3, min(args.steps, 20))
     warm = max(args.warmup, 3)
@@ -329,6 +341,13 @@ def run_ours(args, rank, local_rank, world):
                 fast = tensor_line("prefill8k", rf, world, peaks, "single bf16 (rel-L2 ~1.4e-3)")
                 line["prefill"]["fast_p"] = {"value": fast["value"], "unit": "TFLOP/s", "ms_per_step": fast["ms_per_step"],
                                              "roofline_frac": fast["roofline"]["frac"]}
+            rq = measure("decode", args, rank, world, fused_rows=True)
+            if rank == 0:
+                line["fused_rows"] = {
+                    "what": "the decode step fed by fp32 fused q/k/v projection rows (qw_mixer_forward_fused): scatter, "
+                            "query/gate de-interleave, q/k RMSNorm, rope(k) and append in one launch before attention",
+                    "value": round(rq["kv_bytes_all"] / (rq["ms_per_step"] * 1e-3) / 1e9, 1), "unit": "GB/s",
+                    "ms_per_step": round(rq["ms_per_step"], 5), "gpu_launches_per_step": rq["launches"] // rq["steps"]}
             rv = measure("verify", args, rank, world, with_e2e=False)
             if rank == 0:
                 v = hbm_line("verify", dict(rv, e2e_ms_per_step=rv["ms_per_step"]), world, peaks)

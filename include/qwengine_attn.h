@@ -196,6 +196,18 @@ int qw_last_launch_count(void);
 int qw_profile_enable(int on);
 int qw_profile_last_kernel_ms(float *ms);
 
+/* The fused mixer fed by the layer's fused q/k/v projection, i.e. with the launches that the reference
+ * puts between that GEMM and attention folded in: unpack3 (src/model.cu:221, src/elem.cu:226-237),
+ * k_split_qgate (src/model.cu:223-224, src/mixers.cu:382-390) and the two k_rmsnorm_head launches
+ * (src/model.cu:225-226, src/mixers.cu:393-413; weights are used as 1 + w).  `fused` holds one row per new
+ * token, [ (q[256] | gate[256]) x q_heads | k[kv_heads][256] | v[kv_heads][256] ], fp32 (the reference's GEMM
+ * output, fused_is_f32 = 1) or bf16.  d->q and d->gate are OUTPUT scratch of n_seq * n_new * q_heads * 256 bf16
+ * each (normalised query and gate, consumed by the attention kernel of the same call); d->k_new and d->v_new
+ * are ignored.  d->flags must contain QW_F_APPEND; q_norm_w / k_norm_w are the 256 bf16 weights of q_norm /
+ * k_norm, eps the reference's RMS_EPS (qwen38.h:32).  Same return codes as qw_mixer_forward. */
+int qw_mixer_forward_fused(const qw_mixer_desc *d, const void *fused, int fused_is_f32, const qw_bf16 *q_norm_w,
+                           const qw_bf16 *k_norm_w, float eps, qw_stream stream);
+
 /* ------------------------------------------------------------------------------------------
  * Cross-GPU split-KV combine (used only where one sequence's KV range is split across GPUs)
  *

@@ -307,8 +307,9 @@ void oracle_combine2(const float *o1, float m1, float l1, const float *o2, float
  * k_unpack3 (src/elem.cu:226-237) scatters the three parts, k_split_qgate (src/mixers.cu:382-390)
  * separates query and gate per head, k_rmsnorm_head (src/mixers.cu:393-413) scales every q and k
  * head by rsqrt(mean(x^2) + eps) * (1 + w[d]) with bf16 weights shared by all heads.  Sums in double.
- * round_bf16 != 0 rounds q, gate, k and v to bf16 on the way out: that is where the B200 path stores
- * them (its activations are bf16); 0 keeps the reference's fp32 values. */
+ * round_bf16 != 0 rounds q and gate to bf16 on the way out: that is where the B200 path stores them (its
+ * activations are bf16; k and v are rounded once, when the mixer writes them into a bf16 cache);
+ * 0 keeps the reference's fp32 values. */
 void oracle_fused_rows(const float *fused, int64_t n_rows, int q_heads, int kv_heads, int dim,
                        const uint16_t *q_norm_w, const uint16_t *k_norm_w, double eps, int round_bf16,
                        float *q, float *gate, float *k, float *v) {
@@ -327,7 +328,7 @@ void oracle_fused_rows(const float *fused, int64_t n_rows, int q_heads, int kv_h
       const double sc = 1.0 / sqrt(ss / dim + eps);
       for (int d = 0; d < dim; ++d) {
         const float y = (float)((double)x[d] * sc * (1.0 + (double)bf16_to_f32(w[d])));
-        dst[d] = round_bf16 ? bf16_to_f32(f32_to_bf16(y)) : y;
+        dst[d] = (round_bf16 && is_q) ? bf16_to_f32(f32_to_bf16(y)) : y;
       }
       if (is_q) {
         float *gd = gate + (r * q_heads + h) * dim;
@@ -335,7 +336,7 @@ void oracle_fused_rows(const float *fused, int64_t n_rows, int q_heads, int kv_h
       }
     }
     for (int64_t i = 0; i < (int64_t)kv_heads * dim; ++i)
-      v[r * kv_heads * dim + i] = round_bf16 ? bf16_to_f32(f32_to_bf16(vrow[i])) : vrow[i];
+      v[r * kv_heads * dim + i] = vrow[i];
   }
 }
 

@@ -58,6 +58,7 @@ _SIGS = {
     "qw_mixer_workspace_bytes": (C.c_size_t, [C.POINTER(MixerDesc)]),
     "qw_mixer_forward": (_i, [C.POINTER(MixerDesc), _vp]),
     "qw_mixer_forward_partial": (_i, [C.POINTER(MixerDesc), _vp, _vp]),
+    "qw_mixer_forward_fused": (_i, [C.POINTER(MixerDesc), _vp, _i, _vp, _vp, _f, _vp]),
     "qw_combine_partials": (_i, [_vp, _i, C.c_int64, _i, _vp, _vp, _vp, _i, _vp]),
 }
 
@@ -162,13 +163,13 @@ class Mixer:
         self._keep = None
 
     def bind(self, q, kc, vc, pos, out, k_new=None, v_new=None, gate=None, lse=None, cache_row=None,
-             mpos=None, flags=F_ROPE | F_APPEND | F_GATE):
+             mpos=None, flags=F_ROPE | F_APPEND | F_GATE, fused=False):
         d = self.desc
         if out.dtype == torch.float32:
             flags |= F_OUT_F32
         if gate is None:
             flags &= ~F_GATE
-        if k_new is None:
+        if k_new is None and not fused:  # forward_fused() takes k and v from the fused rows
             flags &= ~F_APPEND
         d.flags = flags
         d.q, d.k_new, d.v_new, d.gate = q.data_ptr(), _addr(k_new), _addr(v_new), _addr(gate)
@@ -180,6 +181,15 @@ class Mixer:
 
     def forward(self, stream=None):
         _check(lib().qw_mixer_forward(C.byref(self.desc), _stream(stream)))
+
+    def forward_fused(self, fused, q_norm_w, k_norm_w, eps=1e-6, stream=None):
+        """The same call fed by the fused q/k/v projection rows [n_seq * n_new, q_heads*512 + 2*kv_heads*256]
+        (float32 or bf16): scatter, query/gate de-interleave and per-head RMSNorm with (1 + w) run inside.
+        The q and gate tensors given to bind() are overwritten with the normalised query and the gate."""
+        assert fused.dtype in (torch.float32, torch.bfloat16) and fused.is_contiguous()
+        assert fused.numel() == self.n_seq * self.n_new * (self.q_heads * 2 + 2 * self.kv_heads) * HEAD_DIM
+        _check(lib().qw_mixer_forward_fused(C.byref(self.desc), _p(fused), 1 if fused.dtype == torch.float32 else 0,
+                                            _p(q_norm_w), _p(k_norm_w), float(eps), _stream(stream)))
 
     def forward_partial(self, partial, stream=None):
         _check(lib().qw_mixer_forward_partial(C.byref(self.desc), _p(partial), _stream(stream)))

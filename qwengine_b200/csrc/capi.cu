@@ -290,17 +290,29 @@ int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   return rc;
 }
 
-bool desc_ok(const qw_mixer_desc *d) {
+// The fused projection rows of qw_mixer_forward_fused, when that is the caller.
+struct FusedRows {
+  const void *rows;
+  bool is_f32;
+  const uint16_t *q_norm_w, *k_norm_w;
+  float eps;
+};
+
+bool desc_ok(const qw_mixer_desc *d, const FusedRows *fr) {
   if (!d || d->n_seq < 0 || d->n_new < 0) return false;
   if (!d->q || !d->out || !d->kc || !d->vc || !d->pos || d->cache_rows <= 0) return false;
-  if ((d->flags & QW_F_APPEND) && (!d->k_new || !d->v_new)) return false;
+  if (fr) {
+    if (!fr->rows || !fr->q_norm_w || !fr->k_norm_w || !d->gate || !(d->flags & QW_F_APPEND)) return false;
+  } else if ((d->flags & QW_F_APPEND) && (!d->k_new || !d->v_new)) {
+    return false;
+  }
   if ((d->flags & QW_F_GATE) && !d->gate) return false;
   return true;
 }
 
-int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) {
+int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, const FusedRows *fr = nullptr) {
   g_launches = 0;
-  if (!desc_ok(d)) return QW_ERR_ARG;
+  if (!desc_ok(d, fr)) return QW_ERR_ARG;
   if (!geometry_ok(d->head_dim, d->kv_heads, d->q_heads) || d->rotary_dim != ROTARY_DIM) return QW_ERR_SHAPE;
   if (d->n_seq == 0 || d->n_new == 0) return QW_OK;
   if ((long long)d->n_seq * d->n_new > (1ll << 30)) return QW_ERR_SHAPE;
@@ -316,7 +328,23 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st) 
   if (!use_umma && !partial && (d->flags & QW_F_APPEND) && d->workspace && d->workspace_bytes > cnt_bytes)
     cnt = reinterpret_cast<int *>(d->workspace);
   const long long n_units = (long long)(cnt_bytes / sizeof(int));
-  if (d->flags & QW_F_APPEND) {
+  if (fr) {
+    const unsigned rows = (unsigned)((size_t)d->n_seq * d->n_new);
+    uint16_t *qo = const_cast<uint16_t *>(d->q), *go = const_cast<uint16_t *>(d->gate);
+    const int do_rope = (d->flags & QW_F_ROPE) ? 1 : 0;
+    if (fr->is_f32)
+      fused_rows_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float *>(fr->rows), fr->q_norm_w, fr->k_norm_w,
+                                                      fr->eps, qo, go, d->kc, d->vc, d->pos, d->cache_row, d->mpos,
+                                                      d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt,
+                                                      cnt ? (int)n_units : 0);
+    else
+      fused_rows_kernel<uint16_t><<<rows, 256, 0, st>>>(static_cast<const uint16_t *>(fr->rows), fr->q_norm_w,
+                                                         fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
+                                                         d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads,
+                                                         do_rope, tab, cnt, cnt ? (int)n_units : 0);
+    int rc = check_launch("fused_rows_kernel");
+    if (rc) return rc;
+  } else if (d->flags & QW_F_APPEND) {
     rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
         d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
         (d->flags & QW_F_ROPE) ? 1 : 0, tab, cnt, cnt ? (int)n_units : 0);
@@ -577,6 +605,14 @@ size_t qw_mixer_workspace_bytes(const qw_mixer_desc *d) {
 }
 int qw_mixer_forward(const qw_mixer_desc *d, qw_stream stream) {
   return mixer_forward_impl(d, nullptr, (cudaStream_t)stream);
+}
+int qw_mixer_forward_fused(const qw_mixer_desc *d, const void *fused, int fused_is_f32, const qw_bf16 *q_norm_w,
+                           const qw_bf16 *k_norm_w, float eps, qw_stream stream) {
+  if ((reinterpret_cast<uintptr_t>(fused) & 15) || (reinterpret_cast<uintptr_t>(q_norm_w) & 15) ||
+      (reinterpret_cast<uintptr_t>(k_norm_w) & 15) || !(eps >= 0.f))
+    return QW_ERR_ARG;
+  const FusedRows fr = {fused, fused_is_f32 != 0, q_norm_w, k_norm_w, eps};
+  return mixer_forward_impl(d, nullptr, (cudaStream_t)stream, &fr);
 }
 int qw_mixer_forward_partial(const qw_mixer_desc *d, float *partial, qw_stream stream) {
   if (!partial) return QW_ERR_ARG;

@@ -73,6 +73,12 @@ struct Mixer {
   }
   size_t workspace_bytes() const { return qw_mixer_workspace_bytes(&d); }
   int forward(cudaStream_t st = 0) const { return qw_mixer_forward(&d, st); }
+  // Fed by the fused projection rows (fp32 as the reference's GEMM emits them): what src/model.cu:221-226
+  // does with unpack3, k_split_qgate and k_rmsnorm_head happens inside the call.
+  int forward_fused(const float *fused, const qw_bf16 *q_norm_w, const qw_bf16 *k_norm_w, float eps = 1e-6f,
+                    cudaStream_t st = 0) const {
+    return qw_mixer_forward_fused(&d, fused, 1, q_norm_w, k_norm_w, eps, st);
+  }
 };
 
 }  // namespace qwengine_b200
