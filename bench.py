@@ -296,7 +296,7 @@ def tensor_line(name, r, world, peaks, mode):
     }
 
 
-def cpu_baseline(w, min_seconds=8.0):
+def cpu_baseline(w, min_seconds=10.0):
     """The CPU oracle timed on a bounded sample of the same workload: whole sequences of the batch,
     repeated until `min_seconds` of CPU work have been done."""
     from oracle import pyoracle as O
@@ -314,7 +314,7 @@ def cpu_baseline(w, min_seconds=8.0):
         O.mixer(q, k, v, g, kc, vc, hist, cache_row, kv_heads=w["kv_heads"])
         passes += 1
         dt = time.perf_counter() - t0
-        if dt >= min_seconds or passes >= 200:
+        if dt >= min_seconds or passes >= 5000:
             break
     nbytes = float(cap.sum()) * KV_BYTES_PER_TOKEN * w["kv_heads"] / 4 * passes
     return {"value": round(nbytes / dt / 1e9, 4), "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
