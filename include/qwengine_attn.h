@@ -180,6 +180,15 @@ typedef struct qw_mixer_desc {
   /* device int that receives a non-zero code if a kernel gave up on a bounded wait; may
    * be NULL.  It is only ever written on error. */
   int *status;
+  /* Paged cache (optional; the reference keeps one contiguous cache per layer, src/model.cu:182-184, and
+   * serves one sequence, README.md:365-367 -- a block table is what a multi-sequence server puts here).
+   * block_table != NULL: the pool is cut into pages of page_rows rows (a multiple of 128) and token t of
+   * sequence s lives in row block_table[s * block_table_stride + t / page_rows] * page_rows + t % page_rows;
+   * cache_row is then ignored.  Device memory, int32, at least ceil((pos[s] + n_new) / page_rows) entries
+   * per sequence.  NULL (a zeroed descriptor) keeps the contiguous layout. */
+  const int *block_table;
+  int block_table_stride;
+  int page_rows;
 } qw_mixer_desc;
 
 size_t qw_mixer_workspace_bytes(const qw_mixer_desc *d);

@@ -31,6 +31,7 @@ class MixerDesc(C.Structure):
         ("q", _vp), ("k_new", _vp), ("v_new", _vp), ("gate", _vp), ("out", _vp), ("lse", _vp),
         ("kc", _vp), ("vc", _vp), ("cache_rows", C.c_int64), ("cache_row", _vp), ("pos", _vp),
         ("mpos", _vp), ("workspace", _vp), ("workspace_bytes", C.c_size_t), ("status", _vp),
+        ("block_table", _vp), ("block_table_stride", _i), ("page_rows", _i),
     ]
 
 
@@ -163,7 +164,7 @@ class Mixer:
         self._keep = None
 
     def bind(self, q, kc, vc, pos, out, k_new=None, v_new=None, gate=None, lse=None, cache_row=None,
-             mpos=None, flags=F_ROPE | F_APPEND | F_GATE, fused=False):
+             mpos=None, flags=F_ROPE | F_APPEND | F_GATE, fused=False, block_table=None, page_rows=0):
         d = self.desc
         if out.dtype == torch.float32:
             flags |= F_OUT_F32
@@ -176,7 +177,11 @@ class Mixer:
         d.out, d.lse, d.kc, d.vc = out.data_ptr(), _addr(lse), kc.data_ptr(), vc.data_ptr()
         d.cache_rows = kc.numel() // (self.kv_heads * HEAD_DIM)
         d.cache_row, d.pos, d.mpos = _addr(cache_row), pos.data_ptr(), _addr(mpos)
-        self._keep = (q, kc, vc, pos, out, k_new, v_new, gate, lse, cache_row, mpos)
+        # paged cache: int32 block table [n_seq, pages per sequence], pages of page_rows (multiple of 128) rows
+        d.block_table = _addr(block_table)
+        d.block_table_stride = 0 if block_table is None else int(block_table.shape[-1])
+        d.page_rows = int(page_rows)
+        self._keep = (q, kc, vc, pos, out, k_new, v_new, gate, lse, cache_row, mpos, block_table)
         return self
 
     def forward(self, stream=None):

@@ -129,6 +129,7 @@ struct AttnCall {
   const uint16_t *kc, *vc;
   int64_t cache_rows;
   const int64_t *cache_row;
+  PageMap pages;
   const int *pos;
   const int *mpos;
   int n_seq, n_new, q_heads, kv_heads;
@@ -186,7 +187,7 @@ int launch_splitkv(const AttnCall &c, cudaStream_t st) {
   SplitKVParams p;
   memset(&p, 0, sizeof(p));
   p.q = c.q; p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.partial_out = c.partial_out;
-  p.pos = c.pos; p.cache_row = c.cache_row; p.mpos = c.mpos; p.ws = c.ws; p.status = c.status;
+  p.pos = c.pos; p.cache_row = c.cache_row; p.pages = c.pages; p.mpos = c.mpos; p.ws = c.ws; p.status = c.status;
   p.cnt = c.partial_out ? nullptr : c.cnt;
   p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.rb = splitkv_rb(c.n_new);
@@ -258,7 +259,7 @@ int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   SplitKVParams p;
   memset(&p, 0, sizeof(p));
   p.q = c.q; p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.partial_out = nullptr;
-  p.pos = c.pos; p.cache_row = c.cache_row; p.mpos = c.mpos; p.ws = c.ws; p.status = c.status; p.cnt = c.cnt;
+  p.pos = c.pos; p.cache_row = c.cache_row; p.pages = c.pages; p.mpos = c.mpos; p.ws = c.ws; p.status = c.status; p.cnt = c.cnt;
   p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.rb = splitkv_umma_rb(c.n_new);
   p.nblk = (c.n_new + p.rb - 1) / p.rb;
@@ -317,6 +318,11 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
   if (d->n_seq == 0 || d->n_new == 0) return QW_OK;
   if ((long long)d->n_seq * d->n_new > (1ll << 30)) return QW_ERR_SHAPE;
   const RopeTable tab = make_rope_table(d->theta, ROTARY_DIM);
+  PageMap pm = {nullptr, 0, 0};
+  if (d->block_table) {
+    if (d->page_rows <= 0 || d->page_rows % 128 || d->block_table_stride <= 0) return QW_ERR_ARG;
+    pm.table = d->block_table; pm.stride = d->block_table_stride; pm.page_rows = d->page_rows;
+  }
   if ((d->flags & QW_F_NO_CAUSAL) && (d->flags & QW_F_APPEND)) return QW_ERR_ARG;  // a sub-range call never owns the new rows
   const bool use_umma =
       !(d->flags & (QW_F_NO_UMMA | QW_F_NO_CAUSAL)) && !partial && prefill_umma_supported(d->n_new);
@@ -336,18 +342,18 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
       fused_rows_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float *>(fr->rows), fr->q_norm_w, fr->k_norm_w,
                                                       fr->eps, qo, go, d->kc, d->vc, d->pos, d->cache_row, d->mpos,
                                                       d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt,
-                                                      cnt ? (int)n_units : 0);
+                                                      cnt ? (int)n_units : 0, pm);
     else
       fused_rows_kernel<uint16_t><<<rows, 256, 0, st>>>(static_cast<const uint16_t *>(fr->rows), fr->q_norm_w,
                                                          fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
                                                          d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads,
-                                                         do_rope, tab, cnt, cnt ? (int)n_units : 0);
+                                                         do_rope, tab, cnt, cnt ? (int)n_units : 0, pm);
     int rc = check_launch("fused_rows_kernel");
     if (rc) return rc;
   } else if (d->flags & QW_F_APPEND) {
     rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
         d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
-        (d->flags & QW_F_ROPE) ? 1 : 0, tab, cnt, cnt ? (int)n_units : 0);
+        (d->flags & QW_F_ROPE) ? 1 : 0, tab, cnt, cnt ? (int)n_units : 0, pm);
     int rc = check_launch("rope_append_kernel");
     if (rc) return rc;
   }
@@ -356,7 +362,7 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
     memset(&pc, 0, sizeof(pc));
     pc.q = d->q; pc.gate = (d->flags & QW_F_GATE) ? d->gate : nullptr; pc.out = d->out;
     pc.out_is_f32 = (d->flags & QW_F_OUT_F32) != 0; pc.lse = d->lse;
-    pc.kc = d->kc; pc.vc = d->vc; pc.cache_rows = d->cache_rows; pc.cache_row = d->cache_row;
+    pc.kc = d->kc; pc.vc = d->vc; pc.cache_rows = d->cache_rows; pc.cache_row = d->cache_row; pc.pages = pm;
     pc.pos = d->pos; pc.mpos = d->mpos; pc.n_seq = d->n_seq; pc.n_new = d->n_new;
     pc.q_heads = d->q_heads; pc.kv_heads = d->kv_heads; pc.scale = d->scale;
     pc.do_rope = (d->flags & QW_F_ROPE) != 0; pc.status = d->status;
@@ -377,7 +383,7 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
   memset(&c, 0, sizeof(c));
   c.q = d->q; c.q_is_f32 = false; c.gate = d->gate; c.out = d->out;
   c.out_is_f32 = (d->flags & QW_F_OUT_F32) != 0; c.lse = d->lse; c.partial_out = partial;
-  c.kc = d->kc; c.vc = d->vc; c.cache_rows = d->cache_rows; c.cache_row = d->cache_row;
+  c.kc = d->kc; c.vc = d->vc; c.cache_rows = d->cache_rows; c.cache_row = d->cache_row; c.pages = pm;
   c.pos = d->pos; c.mpos = d->mpos; c.n_seq = d->n_seq; c.n_new = d->n_new;
   c.q_heads = d->q_heads; c.kv_heads = d->kv_heads; c.theta = d->theta; c.scale = d->scale;
   c.do_rope = (d->flags & QW_F_ROPE) != 0; c.do_gate = (d->flags & QW_F_GATE) != 0;
@@ -462,7 +468,7 @@ const char *qw_strerror(int code) {
     default: return "unknown error code";
   }
 }
-int qw_abi_version(void) { return 1; }
+int qw_abi_version(void) { return 2; }
 const char *qw_last_cuda_error(void) { return g_cuda_err; }
 int qw_last_launch_count(void) { return g_launches; }
 

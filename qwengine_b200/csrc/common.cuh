@@ -82,6 +82,21 @@ __device__ __forceinline__ void rope_sincos_reduced(int pos, double inv_freq, fl
   __sincosf(r, &s, &c);
 }
 
+// Where a sequence's cached tokens live.  Contiguous (table == nullptr): token t of sequence s is row
+// cache_row[s] + t of the pool.  Paged: the pool is cut into pages of page_rows rows (a multiple of 128,
+// so no K/V tile straddles a page) and token t is row table[s * stride + t / page_rows] * page_rows +
+// t % page_rows -- a block table as serving engines keep it, one line per sequence.
+struct PageMap {
+  const int *table;
+  int stride;
+  int page_rows;
+};
+__device__ __forceinline__ long long cache_row_of(const PageMap &pm, const int64_t *cache_row, int s, int t) {
+  if (!pm.table) return (cache_row ? cache_row[s] : 0) + t;
+  const int pg = t / pm.page_rows;
+  return (long long)pm.table[(size_t)s * pm.stride + pg] * pm.page_rows + (t - pg * pm.page_rows);
+}
+
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
 // Same value to ~2 ulp with the approximate reciprocal: for epilogues that are instruction-bound.
 __device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }

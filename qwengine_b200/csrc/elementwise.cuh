@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const uint16_t *k_new,
                                                           uint16_t *vc, const int *pos, const int64_t *cache_row,
                                                           const int *mpos, int n_new, int kv_heads, int do_rope,
                                                           const __grid_constant__ RopeTable tab, int *zero_ints,
-                                                          int n_zero) {
+                                                          int n_zero, PageMap pages) {
   // block 0 also clears the split-KV arrival counters of the attention launch that follows
   if (blockIdx.x == 0)
     for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero_ints[i] = 0;
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const uint16_t *k_new,
   const int h = threadIdx.x >> 5, c16 = threadIdx.x & 31;
   if (h >= kv_heads) return;
   const size_t src = (r * kv_heads + h) * HEAD_DIM + c16 * 8;
-  const size_t dst = ((size_t)((cache_row ? cache_row[s] : 0) + pz) * kv_heads + h) * HEAD_DIM + c16 * 8;
+  const size_t dst = ((size_t)cache_row_of(pages, cache_row, s, pz) * kv_heads + h) * HEAD_DIM + c16 * 8;
   *reinterpret_cast<uint4 *>(vc + dst) = *reinterpret_cast<const uint4 *>(v_new + src);
   if (!do_rope || c16 >= 8) {
     *reinterpret_cast<uint4 *>(kc + dst) = *reinterpret_cast<const uint4 *>(k_new + src);
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(256) fused_rows_kernel(const TIn *fused, const
                                                          const int64_t *cache_row, const int *mpos, int n_new,
                                                          int q_heads, int kv_heads, int do_rope,
                                                          const __grid_constant__ RopeTable tab, int *zero_ints,
-                                                         int n_zero) {
+                                                         int n_zero, PageMap pages) {
   if (blockIdx.x == 0)
     for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero_ints[i] = 0;
   __shared__ double cs[ROT_PAIRS][2];
@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(256) fused_rows_kernel(const TIn *fused, const
   const size_t width = (size_t)q_heads * 2 * HEAD_DIM + 2 * (size_t)kv_heads * HEAD_DIM;
   const TIn *row = fused + r * width;
   const TIn *krow = row + (size_t)q_heads * 2 * HEAD_DIM, *vrow = krow + (size_t)kv_heads * HEAD_DIM;
-  const size_t crow = ((size_t)((cache_row ? cache_row[s] : 0) + pz) * kv_heads) * HEAD_DIM;
+  const size_t crow = ((size_t)cache_row_of(pages, cache_row, s, pz) * kv_heads) * HEAD_DIM;
   float w8[8];
   // ---- query heads and their gates ----
   load8<uint16_t>(q_norm_w + lane * 8, w8);

@@ -81,7 +81,6 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   const int q0 = qt * PF_BM;
   const int rows_valid = min(PF_BM, p.n_new - q0);
   const int pos = p.pos[s];
-  const long long crow = p.cache_row ? p.cache_row[s] : 0;
   const int kv_len = pos + q0 + rows_valid;           // keys visible to the last row of the tile
   const int nt = (kv_len + PF_BN - 1) / PF_BN;        // KV tiles
 
@@ -134,7 +133,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
             break;
           }
           mbar_expect_tx(&ctl->slot_full[sl], PF_SLOT);
-          tma_load_2d(ring + sl * PF_SLOT, &mapK, &ctl->slot_full[sl], kvh * HEAD_DIM + c * 64, (int)(crow + j * PF_BN));
+          tma_load_2d(ring + sl * PF_SLOT, &mapK, &ctl->slot_full[sl], kvh * HEAD_DIM + c * 64, (int)cache_row_of(p.pages, p.cache_row, s, j * PF_BN));
         }
       };
       auto load_v = [&](int j) {
@@ -150,7 +149,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 #pragma unroll
           for (int c = 0; c < 4; ++c)  // 32 keys x 64 channels each, channel atoms 4 KB apart
             tma_load_2d(ring + sl * PF_SLOT + c * 4096, &mapV, &ctl->slot_full[sl], kvh * HEAD_DIM + c * 64,
-                        (int)(crow + j * PF_BN + g * 32));
+                        (int)cache_row_of(p.pages, p.cache_row, s, j * PF_BN + g * 32));
         }
       };
       for (int j = 0; j <= nt && ok; ++j) {
@@ -442,7 +441,7 @@ int launch_prefill_umma(const PrefillCall &c, cudaStream_t st, int *n_launched) 
     return 1;
   PrefillParams p;
   memset(&p, 0, sizeof(p));
-  p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.cache_row = c.cache_row; p.pos = c.pos; p.mpos = c.mpos;
+  p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.cache_row = c.cache_row; p.pages = c.pages; p.pos = c.pos; p.mpos = c.mpos;
   p.status = c.status; p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.n_qtiles = (c.n_new + PF_BM - 1) / PF_BM;
   p.scale_log2 = c.scale * LOG2E;

@@ -14,6 +14,7 @@ struct PrefillCall {
   const uint16_t *kc, *vc;
   int64_t cache_rows;
   const int64_t *cache_row;
+  qwb::PageMap pages;   // block table, if the cache is paged
   const int *pos;
   const int *mpos;
   int n_seq, n_new, q_heads, kv_heads;

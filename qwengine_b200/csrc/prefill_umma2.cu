@@ -172,7 +172,6 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
   const int q0 = qt * P2_BM;
   const int rows_valid = min(P2_BM, p.n_new - q0);
   const int pos = p.pos[s];
-  const long long crow = p.cache_row ? p.cache_row[s] : 0;
   const int kv_len = pos + q0 + rows_valid;
   const int nt = (kv_len + P2_BN - 1) / P2_BN;
 
@@ -246,7 +245,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
             }
             const uint32_t bar = map_to_cta(smem_u32(&ctl->slot_full[sl]), 0);
             remote_arrive_expect_tx(bar, P2_SLOT);
-            const int krow = (int)(crow + j * P2_BN + (int)rank * 64);
+            const int krow = (int)cache_row_of(p.pages, p.cache_row, s, j * P2_BN + (int)rank * 64);
 #pragma unroll
             for (int a = 0; a < 2; ++a)
               tma_load_2d_pair(ring + sl * P2_SLOT + a * 8192, &mapK, bar, kvh * HEAD_DIM + (2 * i + a) * 64, krow);
@@ -263,7 +262,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
             }
             const uint32_t bar = map_to_cta(smem_u32(&ctl->slot_full[sl]), 0);
             remote_arrive_expect_tx(bar, P2_SLOT);
-            const int vrow = (int)(crow + (j - 1) * P2_BN + g * 64);
+            const int vrow = (int)cache_row_of(p.pages, p.cache_row, s, (j - 1) * P2_BN + g * 64);
 #pragma unroll
             for (int a = 0; a < 2; ++a)
               tma_load_2d_pair(ring + sl * P2_SLOT + a * 8192, &mapV, bar, kvh * HEAD_DIM + (int)rank * 128 + a * 64, vrow);
@@ -286,7 +285,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         ok = __all_sync(0xffffffffu, ok);
         if (ok && elect_one()) {
           mbar_expect_tx(&ctl->fix_bar, P2_SLOT);
-          const int vrow = (int)(crow + (nt - 1) * P2_BN + g * 64);
+          const int vrow = (int)cache_row_of(p.pages, p.cache_row, s, (nt - 1) * P2_BN + g * 64);
 #pragma unroll
           for (int a = 0; a < 2; ++a)
             tma_load_2d(ring + sl * P2_SLOT + a * 8192, &mapV, &ctl->fix_bar, kvh * HEAD_DIM + (int)rank * 128 + a * 64, vrow);
@@ -627,7 +626,7 @@ int launch_prefill_umma_pair(const PrefillCall &c, cudaStream_t st, int *n_launc
   if (c.q_heads % 2) return 2;
   PrefillParams p;
   memset(&p, 0, sizeof(p));
-  p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.cache_row = c.cache_row; p.pos = c.pos; p.mpos = c.mpos;
+  p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.cache_row = c.cache_row; p.pages = c.pages; p.pos = c.pos; p.mpos = c.mpos;
   p.status = c.status; p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.n_qtiles = (c.n_new + P2_BM - 1) / P2_BM;
   p.scale_log2 = c.scale * LOG2E;

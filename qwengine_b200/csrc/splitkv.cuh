@@ -37,6 +37,7 @@ struct SplitKVParams {
   float *partial_out;     // non-null: emit (o, m, l) per (row, head) instead of out / lse
   const int *pos;         // [n_seq]
   const int64_t *cache_row;  // [n_seq] or null
+  PageMap pages;             // block table, if the cache is paged
   const int *mpos;        // [n_seq][n_new][3] or null
   float *ws;              // (G + n_units) slots of rb*6*PART_STRIDE floats
   int *cnt;               // per-unit arrival counters (zero at launch) or null: merge in a second kernel
@@ -338,10 +339,9 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
           pok = false;
           return false;
         }
-        const long long row0 = p.cache_row ? p.cache_row[ui.s] : 0;
         uint8_t *kd = stage_base + st * SK_STAGE_BYTES, *vd = kd + SK_TILE_BYTES;
         mbar_expect_tx(&full[st], SK_STAGE_BYTES);
-        const int r = (int)(row0 + (long long)pt * SK_TK);
+        const int r = (int)cache_row_of(p.pages, p.cache_row, ui.s, pt * SK_TK);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           tma_load_2d(kd + c * (SK_TK * 128), &mapK, &full[st], ui.kvh * HEAD_DIM + c * 64, r);
@@ -436,12 +436,12 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
           const size_t trow = (size_t)ui.s * p.n_new + ui.tok0 + b;
           const size_t grow = trow * p.q_heads + (size_t)ui.kvh * GROUP + hh;
           const TIn *src = reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM;
-          const double x = load_as_f32<TIn>(src + i), y = load_as_f32<TIn>(src + i + ROT_PAIRS);
+          const float x = load_as_f32<TIn>(src + i), y = load_as_f32<TIn>(src + i + ROT_PAIRS);
           const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.pos + ui.tok0 + b;
-          double c, sn;
-          rope_sincos_exact(pz, p.rope.inv_freq[i], c, sn);
-          xr = (float)(x * c - y * sn);
-          yr = (float)(x * sn + y * c);
+          float c, sn;
+          rope_sincos_reduced(pz, p.rope.inv_freq[i], c, sn);  // angle reduced in double, then the fast sincos
+          xr = x * c - y * sn;
+          yr = x * sn + y * c;
         }
         const uint16_t xh = f32_to_bf16_bits(xr), yh = f32_to_bf16_bits(yr);
         *reinterpret_cast<uint16_t *>(qregion + q_hi_off(row, i)) = xh;

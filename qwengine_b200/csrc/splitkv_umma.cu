@@ -168,14 +168,13 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       int nt, t0, t1;
       while (ok && find_live(u, pre, nt, t0, t1)) {
         const UnitInfo ui = unit_info(p, u);
-        const long long row0 = p.cache_row ? p.cache_row[ui.s] : 0;
         for (int j = t0; j <= t1 && ok; ++j) {
           if (j < t1) {
             QWB_TL(10, j - t0);
             for (int c = 0; c < 4 && ok; ++c) {
               if (!slot_ready()) break;
               tma_load_2d(ring + sl * DU_SLOT, &mapK, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
-                          (int)(row0 + (long long)j * DU_BN));
+                          (int)cache_row_of(p.pages, p.cache_row, ui.s, j * DU_BN));
               advance();
             }
           }
@@ -186,7 +185,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
 #pragma unroll
               for (int c = 0; c < 4; ++c)  // 32 keys x 64 channels each, channel atoms 4 KB apart
                 tma_load_2d(ring + sl * DU_SLOT + c * 4096, &mapV, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
-                            (int)(row0 + (long long)(j - 1) * DU_BN + g * 32));
+                            (int)cache_row_of(p.pages, p.cache_row, ui.s, (j - 1) * DU_BN + g * 32));
               advance();
             }
           }

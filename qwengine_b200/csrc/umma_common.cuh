@@ -29,6 +29,7 @@ struct PrefillParams {
   void *out;
   float *lse;
   const int64_t *cache_row;
+  PageMap pages;
   const int *pos;
   const int *mpos;
   int *status;
