@@ -172,6 +172,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   }
   return false;
 }
+// Untiled bulk copy global -> shared::cta, completion counted on an mbarrier.  Both addresses 16-byte
+// aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 // 16-byte asynchronous copy global -> shared (no registers held while in flight) and its wait.
 __device__ __forceinline__ void cp_async16(void *dst_smem, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");

@@ -4,6 +4,8 @@ import ctypes
 import os
 import re
 
+import pytest
+
 from qwengine_b200 import api, build
 from tests.conftest import ROOT
 
@@ -48,3 +50,22 @@ def test_argument_validation_needs_no_gpu():
     assert l.qw_rope_f32(p, 24, 128, 64, p, 1e7, None, 1, None) == 2               # head_dim 128 unsupported
     assert l.qw_attn_decode_f32(p, p, p, p, p, 256, 3, 18, 0.0625, p, 64, 1, None) == 2   # 3 kv heads
     assert l.qw_attn_decode_f32(p, p, p, p, p, 256, 4, 24, 0.0625, p, 64, 9, None) == 2   # B > 8
+
+
+def test_header_is_plain_c_and_cpp_mirror_compiles():
+    """include/qwengine_attn.h must parse as C99 (the boundary is a C ABI) and the C++ mirror of the
+    reference's launchers must compile against it."""
+    import shutil
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if shutil.which("gcc") is None or shutil.which("g++") is None:
+        pytest.skip("no host compiler")
+    hdr = os.path.join(root, "include", "qwengine_attn.h")
+    subprocess.check_call(["gcc", "-std=c99", "-fsyntax-only", "-x", "c", hdr])
+    cuda_inc = "/usr/local/cuda/include"
+    if not os.path.isdir(cuda_inc):
+        pytest.skip("no CUDA headers for the C++ mirror")
+    src = "#include \"%s\"\nint main() { qwengine_b200::Mixer m(1, 1); return m.workspace_bytes() == 0; }\n" % os.path.join(
+        root, "qwengine_b200", "csrc", "mixer.hpp")
+    subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-I", os.path.join(root, "include"), "-I", cuda_inc, "-x", "c++", "-"],
+                   input=src.encode(), check=True)
