@@ -311,6 +311,21 @@ bool desc_ok(const qw_mixer_desc *d, const FusedRows *fr) {
   return true;
 }
 
+// The append kernels run right in front of an attention kernel that takes nearly all of an SM's shared
+// memory.  Asking for the same carve-out here spares the SMs a reconfiguration of the L1 / shared
+// split between the two launches of a step.
+void prefer_max_shared_once() {
+  static bool done[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
+  done[dev] = true;
+  cudaFuncSetAttribute(rope_append_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(fused_rows_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(fused_rows_kernel<uint16_t>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);
+  cudaGetLastError();  // a refusal of the hint is harmless
+}
+
 int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, const FusedRows *fr = nullptr) {
   g_launches = 0;
   if (!desc_ok(d, fr)) return QW_ERR_ARG;
@@ -318,6 +333,7 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
   if (d->n_seq == 0 || d->n_new == 0) return QW_OK;
   if ((long long)d->n_seq * d->n_new > (1ll << 30)) return QW_ERR_SHAPE;
   const RopeTable tab = make_rope_table(d->theta, ROTARY_DIM);
+  prefer_max_shared_once();
   PageMap pm = {nullptr, 0, 0};
   if (d->block_table) {
     if (d->page_rows <= 0 || d->page_rows % 128 || d->block_table_stride <= 0) return QW_ERR_ARG;
@@ -339,12 +355,12 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
     uint16_t *qo = const_cast<uint16_t *>(d->q), *go = const_cast<uint16_t *>(d->gate);
     const int do_rope = (d->flags & QW_F_ROPE) ? 1 : 0;
     if (fr->is_f32)
-      fused_rows_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float *>(fr->rows), fr->q_norm_w, fr->k_norm_w,
+      fused_rows_kernel<float><<<dim3(rows, (unsigned)d->kv_heads), 256, 0, st>>>(static_cast<const float *>(fr->rows), fr->q_norm_w, fr->k_norm_w,
                                                       fr->eps, qo, go, d->kc, d->vc, d->pos, d->cache_row, d->mpos,
                                                       d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt,
                                                       cnt ? (int)n_units : 0, pm);
     else
-      fused_rows_kernel<uint16_t><<<rows, 256, 0, st>>>(static_cast<const uint16_t *>(fr->rows), fr->q_norm_w,
+      fused_rows_kernel<uint16_t><<<dim3(rows, (unsigned)d->kv_heads), 256, 0, st>>>(static_cast<const uint16_t *>(fr->rows), fr->q_norm_w,
                                                          fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
                                                          d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads,
                                                          do_rope, tab, cnt, cnt ? (int)n_units : 0, pm);

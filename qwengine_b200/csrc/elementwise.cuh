@@ -99,12 +99,14 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const uint16_t *k_new,
 // unpack3 (src/elem.cu:226-237), k_split_qgate (src/mixers.cu:382-390), both k_rmsnorm_head launches
 // (src/mixers.cu:393-413, weights used as 1 + w), rope(k) and k_kv_append (src/model.cu:219-235).
 // Row layout: [ (q[256] | gate[256]) x q_heads | k[kv_heads][256] | v[kv_heads][256] ].
-// One block of 8 warps per token row; a warp takes whole heads, a lane 8 channels.
+// Grid (token rows, kv_heads), 8 warps: block (r, g) takes KV head g of row r and the six query heads
+// that share it -- warps 0..5 one query head (and its gate) each, warp 6 the key head, warp 7 the value
+// head; a lane holds 8 channels.
 //   q heads: fp32 mean square, q * rsqrt(ms + eps) * (1 + w) -> bf16 q_out; gate -> bf16 gate_out
 //            (q is rotated later, in the attention prologue)
-//   k heads: mean square, scale and rotation in double, rounded once into the bf16 cache row
-//   v:       copied into the bf16 cache row
-// Block 0 also clears the split-KV arrival counters, like rope_append_kernel.
+//   k head:  mean square, scale and rotation in double, rounded once into the bf16 cache row
+//   v head:  copied into the bf16 cache row
+// Block (0, 0) also clears the split-KV arrival counters, like rope_append_kernel.
 template <typename TIn>
 __global__ void __launch_bounds__(256) fused_rows_kernel(const TIn *fused, const uint16_t *q_norm_w,
                                                          const uint16_t *k_norm_w, float eps, uint16_t *q_out,
@@ -113,30 +115,22 @@ __global__ void __launch_bounds__(256) fused_rows_kernel(const TIn *fused, const
                                                          int q_heads, int kv_heads, int do_rope,
                                                          const __grid_constant__ RopeTable tab, int *zero_ints,
                                                          int n_zero, PageMap pages) {
-  if (blockIdx.x == 0)
+  if (blockIdx.x == 0 && blockIdx.y == 0)
     for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero_ints[i] = 0;
-  __shared__ double cs[ROT_PAIRS][2];
   const size_t r = blockIdx.x;  // flat row s * n_new + b
+  const int g = blockIdx.y;     // KV head
   const int s = (int)(r / n_new), b = (int)(r % n_new);
-  const int pz = pos[s] + b;
-  if (do_rope && threadIdx.x < ROT_PAIRS) {
-    const int i = threadIdx.x;
-    const int pp = mpos ? mpos[r * 3 + mrope_component(i)] : pz;
-    rope_sincos_exact(pp, tab.inv_freq[i], cs[i][0], cs[i][1]);
-  }
-  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t width = (size_t)q_heads * 2 * HEAD_DIM + 2 * (size_t)kv_heads * HEAD_DIM;
   const TIn *row = fused + r * width;
-  const TIn *krow = row + (size_t)q_heads * 2 * HEAD_DIM, *vrow = krow + (size_t)kv_heads * HEAD_DIM;
-  const size_t crow = ((size_t)cache_row_of(pages, cache_row, s, pz) * kv_heads) * HEAD_DIM;
   float w8[8];
-  // ---- query heads and their gates ----
-  load8<uint16_t>(q_norm_w + lane * 8, w8);
-  for (int h = warp; h < q_heads; h += 8) {
-    float x[8], g[8];
+  if (warp < GROUP) {
+    // ---- one query head and its gate ----
+    const int h = g * GROUP + warp;
+    float x[8], gt[8];
     load8<TIn>(row + (size_t)h * 2 * HEAD_DIM + lane * 8, x);
-    load8<TIn>(row + (size_t)h * 2 * HEAD_DIM + HEAD_DIM + lane * 8, g);
+    load8<TIn>(row + (size_t)h * 2 * HEAD_DIM + HEAD_DIM + lane * 8, gt);
+    load8<uint16_t>(q_norm_w + lane * 8, w8);
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
@@ -146,45 +140,48 @@ __global__ void __launch_bounds__(256) fused_rows_kernel(const TIn *fused, const
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] = x[j] * sc * (1.0f + w8[j]);
     store8<uint16_t>(q_out + (r * q_heads + h) * HEAD_DIM + lane * 8, x);
-    store8<uint16_t>(gate_out + (r * q_heads + h) * HEAD_DIM + lane * 8, g);
+    store8<uint16_t>(gate_out + (r * q_heads + h) * HEAD_DIM + lane * 8, gt);
+    return;
   }
-  // ---- key heads: normalise, rotate, append ----
+  const int pz = pos[s] + b;
+  const size_t crow = ((size_t)cache_row_of(pages, cache_row, s, pz) * kv_heads + g) * HEAD_DIM;
+  if (warp == GROUP + 1) {
+    // ---- value head ----
+    float x[8];
+    load8<TIn>(row + (size_t)q_heads * 2 * HEAD_DIM + (size_t)(kv_heads + g) * HEAD_DIM + lane * 8, x);
+    store8<uint16_t>(vc + crow + lane * 8, x);
+    return;
+  }
+  // ---- key head: normalise, rotate, append ----
+  float x[8];
+  load8<TIn>(row + (size_t)q_heads * 2 * HEAD_DIM + (size_t)g * HEAD_DIM + lane * 8, x);
   load8<uint16_t>(k_norm_w + lane * 8, w8);
-  for (int h = warp; h < kv_heads; h += 8) {
-    float x[8];
-    load8<TIn>(krow + (size_t)h * HEAD_DIM + lane * 8, x);
-    double ss = 0.0;
+  double cs = 1.0, sn = 0.0;  // lane i: cos / sin of rotary pair i
+  if (do_rope) {
+    const int pp = mpos ? mpos[r * 3 + mrope_component(lane)] : pz;
+    rope_sincos_exact(pp, tab.inv_freq[lane], cs, sn);
+  }
+  double ss = 0.0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) ss += (double)x[j] * (double)x[j];
+  for (int j = 0; j < 8; ++j) ss += (double)x[j] * (double)x[j];
 #pragma unroll
-    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const double sc = 1.0 / sqrt(ss / HEAD_DIM + (double)eps);
+  for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const double sc = 1.0 / sqrt(ss / HEAD_DIM + (double)eps);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] = (float)((double)x[j] * sc * (1.0 + (double)w8[j]));
-    if (do_rope) {
-      // rotary pair (i, i + 32): lanes 0..3 hold i = 0..31, lanes 4..7 hold i + 32
-      float y[8];
+  for (int j = 0; j < 8; ++j) x[j] = (float)((double)x[j] * sc * (1.0 + (double)w8[j]));
+  if (do_rope) {
+    // rotary pair (i, i + 32): lanes 0..3 hold i = 0..31 (8 each), lanes 4..7 hold i + 32
+    const bool lo = lane < 4;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) y[j] = __shfl_xor_sync(0xffffffffu, x[j], 4);
-      if (lane < 8) {
-        const bool lo = lane < 4;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int i = (lane & 3) * 8 + j;
-          const double c = cs[i][0], sn = cs[i][1];
-          const double a = lo ? (double)x[j] : (double)y[j], bq = lo ? (double)y[j] : (double)x[j];  // (x_i, x_{i+32})
-          x[j] = lo ? (float)(a * c - bq * sn) : (float)(a * sn + bq * c);
-        }
-      }
+    for (int j = 0; j < 8; ++j) {
+      const float y = __shfl_xor_sync(0xffffffffu, x[j], 4);
+      const int i = (lane & 3) * 8 + j;
+      const double c = __shfl_sync(0xffffffffu, cs, i), sv = __shfl_sync(0xffffffffu, sn, i);
+      const double a = lo ? (double)x[j] : (double)y, bq = lo ? (double)y : (double)x[j];  // (x_i, x_{i+32})
+      if (lane < 8) x[j] = lo ? (float)(a * c - bq * sv) : (float)(a * sv + bq * c);
     }
-    store8<uint16_t>(kc + crow + (size_t)h * HEAD_DIM + lane * 8, x);
   }
-  // ---- values ----
-  for (int i = threadIdx.x * 8; i < kv_heads * HEAD_DIM; i += 256 * 8) {
-    float x[8];
-    load8<TIn>(vrow + i, x);
-    store8<uint16_t>(vc + crow + i, x);
-  }
+  store8<uint16_t>(kc + crow + lane * 8, x);
 }
 
 }  // namespace qwb
