@@ -135,6 +135,7 @@ struct AttnCall {
   int n_seq, n_new, q_heads, kv_heads;
   float theta, scale;
   bool do_rope, do_gate, no_causal;
+  bool q_dep;  // q / gate are produced by the launch before the attention kernel (fused projection rows)
   float *ws;
   size_t ws_floats;
   int *cnt;  // zeroed arrival counters (one per unit) or null
@@ -160,7 +161,8 @@ int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKV
     configured[dev] = true;
   }
   prof_mark(0, st);
-  kern<<<p.G, (SK_KS * DS + (FOLD ? 0 : 1)) * 32, smem, st>>>(mk, mv, p);
+  // with arrival counters the launch follows this step's append kernel: start while that one still runs
+  launch_kernel(kern, dim3(p.G), dim3((SK_KS * DS + (FOLD ? 0 : 1)) * 32), smem, st, p.cnt != nullptr, mk, mv, p);
   prof_mark(1, st);
   int rc = check_launch("splitkv_kernel");
   if (rc) return rc;
@@ -202,7 +204,7 @@ int launch_splitkv(const AttnCall &c, cudaStream_t st) {
   p.G = (int)G;
   p.q_lo_dims = c.q_is_f32 ? HEAD_DIM : (c.do_rope ? ROTARY_DIM : 0);
   p.scale_log2 = c.scale * LOG2E;
-  p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate; p.no_causal = c.no_causal;
+  p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate; p.no_causal = c.no_causal; p.q_dep = c.q_dep;
   p.rope = make_rope_table(c.theta, ROTARY_DIM);
 
   CUtensorMap mk, mv;
@@ -273,7 +275,7 @@ int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   p.G = (int)G;
   p.q_lo_dims = c.do_rope ? ROTARY_DIM : 0;
   p.scale_log2 = c.scale * LOG2E;
-  p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate; p.no_causal = c.no_causal;
+  p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate; p.no_causal = c.no_causal; p.q_dep = c.q_dep;
   p.rope = make_rope_table(c.theta, ROTARY_DIM);
   CUtensorMap mk, mv;
   int rc = make_rowmajor_map(&mk, c.kc, c.cache_rows, c.kv_heads * HEAD_DIM, 128);
@@ -284,7 +286,7 @@ int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   p.dbg = qwb::g_timeline_buf; p.dbg_block = qwb::g_timeline_block;
 #endif
   prof_mark(0, st);
-  rc = launch_splitkv_umma(mk, mv, p, c.out_is_f32, st);
+  rc = launch_splitkv_umma(mk, mv, p, c.out_is_f32, st, p.cnt != nullptr);
   prof_mark(1, st);
   ++g_launches;
   if (rc == QW_ERR_CUDA) return cuda_fail(cudaGetLastError(), "splitkv_umma_kernel");
@@ -404,6 +406,7 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
   c.q_heads = d->q_heads; c.kv_heads = d->kv_heads; c.theta = d->theta; c.scale = d->scale;
   c.do_rope = (d->flags & QW_F_ROPE) != 0; c.do_gate = (d->flags & QW_F_GATE) != 0;
   c.no_causal = (d->flags & QW_F_NO_CAUSAL) != 0;
+  c.q_dep = fr != nullptr;
   if (!d->workspace || (reinterpret_cast<uintptr_t>(d->workspace) & 15) || d->workspace_bytes <= cnt_bytes)
     return QW_ERR_WORKSPACE;
   c.ws = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(d->workspace) + cnt_bytes);

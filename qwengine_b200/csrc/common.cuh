@@ -172,6 +172,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   }
   return false;
 }
+// Programmatic dependent launch.  The append kernel of a step calls grid_dep_launch_dependents() first thing,
+// which lets the attention kernel launched behind it (with the stream-serialisation attribute) start while
+// the append still runs; the attention kernel calls grid_dep_wait() only where it first needs the append's
+// results: before it loads a tile that holds new rows, and before it takes an arrival ticket (the append
+// kernel clears the counters).  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Untiled bulk copy global -> shared::cta, completion counted on an mbarrier.  Both addresses 16-byte
 // aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_load(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
@@ -240,6 +248,23 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Host side: kernel launch, optionally as a programmatic dependent of the launch before it on the stream.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool dependent,
+                                 Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 }  // namespace qwb

@@ -53,6 +53,7 @@ struct SplitKVParams {
   int nslot;              // tcgen05 kernel: 16 KB ring slots that fit beside that Q tile
   unsigned long long *dbg;  // timeline probe (only written when built with QWB_TIMELINE)
   int dbg_block;
+  int q_dep;              // q and gate are written by the launch before this one (fused projection rows)
   int no_causal;          // every row sees exactly pos[s] keys (a KV sub-range without the new rows)
   RopeTable rope;
 };
@@ -326,7 +327,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   long long ppre = seg[1];                           // flat index of that unit's tile 0
   int pt = (int)(max(g0, ppre) - ppre);              // next tile within the unit
   uint32_t pit = 0;                                  // tiles issued so far
-  bool pok = true;
+  bool pok = true, dep_waited = false;
   auto produce_one = [&]() -> bool {
     while (ppre < g1 && pu < n_units) {
       const UnitInfo ui = unit_info(p, pu);
@@ -338,6 +339,11 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
           if (p.status) *p.status = DEV_ERR_EMPTY_WAIT;
           pok = false;
           return false;
+        }
+        // the first tile that holds rows written by the append kernel of this step: wait for that kernel
+        if (!dep_waited && (pt + 1) * SK_TK > ui.pos) {
+          grid_dep_wait();
+          dep_waited = true;
         }
         uint8_t *kd = stage_base + st * SK_STAGE_BYTES, *vd = kd + SK_TILE_BYTES;
         mbar_expect_tx(&full[st], SK_STAGE_BYTES);
@@ -408,6 +414,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     const bool whole = (t0 == 0 && t1 == nt_unit);
 
     // ---- stage Q: rotate, split into bf16 hi (+ lo), zero the padding rows ----
+    if (p.q_dep) grid_dep_wait();  // q comes out of the launch before this one
     consumer_sync(NCT);  // the previous segment is done with this region
     for (int idx = tid; idx < ROWS * 32; idx += NCT) {
       const int row = idx >> 5, c16 = idx & 31;  // 8 channels d = c16*8 .. +7
@@ -713,7 +720,10 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     if (!whole && p.cnt) {
       __threadfence();  // this thread's partial stores are visible device-wide before the ticket
       consumer_sync(NCT);
-      if (tid == 0) *ticket = atomicAdd(&p.cnt[u], 1);
+      if (tid == 0) {
+        grid_dep_wait();  // the append kernel of this step clears the counters
+        *ticket = atomicAdd(&p.cnt[u], 1);
+      }
       consumer_sync(NCT);
       const int c_first = cta_of_tile(pre, total, G), c_last = cta_of_tile(pre + nt_unit - 1, total, G);
       int nparts = 0;

@@ -154,7 +154,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       long long pre = ctl->part[1];
       int sl = 0;            // ring position: slot, and the parity of the slot's current use
       uint32_t ph = 0;
-      bool wrapped = false, ok = true;
+      bool wrapped = false, ok = true, dep_waited = false;
       auto slot_ready = [&]() -> bool {
         if (wrapped && !wait_or_abort(&ctl->slot_empty[sl], ph ^ 1, abort_flag)) {
           fail(DEV_ERR_EMPTY_WAIT);
@@ -173,6 +173,10 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         for (int j = t0; j <= t1 && ok; ++j) {
           if (j < t1) {
             QWB_TL(10, j - t0);
+            if (!dep_waited && (j + 1) * DU_BN > ui.pos) {  // first tile with rows of this step's append kernel
+              grid_dep_wait();
+              dep_waited = true;
+            }
             for (int c = 0; c < 4 && ok; ++c) {
               if (!slot_ready()) break;
               tma_load_2d(ring + sl * DU_SLOT, &mapK, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
@@ -311,6 +315,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     // value and its bf16 remainder.
     auto stage_q = [&](const UnitInfo &ui) {
       const int R = ui.ntok * GROUP;
+      if (p.q_dep) grid_dep_wait();  // q comes out of the launch before this one
       for (int idx = st_tid; idx < p.q_rows_pad * 32; idx += DU_SM_THREADS) {
         const int r = idx >> 5, c16 = idx & 31;           // 8 channels c16*8 .. +7
         if (p.do_rope && c16 < 8) continue;               // rotary channels are written pair-wise below
@@ -560,6 +565,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       if (tid == 64) QWB_TL(30, 51);
       if (st_tid == 0) {  // one thread decides, so that a failure flagged meanwhile cannot split the group
         const int go = *abort_flag ? 0 : 1;
+        grid_dep_wait();  // the append kernel of this step clears the counters
         for (int k = 0; k < n_pend && go; ++k) {
           const int c_first = cta_of_tile(pend_pre[k] + LEAD, total, G), c_last = cta_of_tile(pend_pre[k] + LEAD + pend_nt[k] - 1, total, G);
           int nparts = 0;
@@ -672,7 +678,7 @@ void splitkv_umma_layout(int rb, int *q_rows_pad, int *nslot) {
 }
 
 int launch_splitkv_umma(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, bool out_is_f32,
-                        cudaStream_t st) {
+                        cudaStream_t st, bool dependent) {
   constexpr size_t smem = 1024 + DU_SMEM_TOTAL;
   static bool configured[64] = {false};
   int dev = 0;
@@ -684,9 +690,9 @@ int launch_splitkv_umma(const CUtensorMap &mk, const CUtensorMap &mv, const Spli
     configured[dev] = true;
   }
   if (out_is_f32)
-    splitkv_umma_kernel<float><<<p.G, DU_THREADS, smem, st>>>(mk, mv, p);
+    launch_kernel(splitkv_umma_kernel<float>, dim3(p.G), dim3(DU_THREADS), smem, st, dependent, mk, mv, p);
   else
-    splitkv_umma_kernel<uint16_t><<<p.G, DU_THREADS, smem, st>>>(mk, mv, p);
+    launch_kernel(splitkv_umma_kernel<uint16_t>, dim3(p.G), dim3(DU_THREADS), smem, st, dependent, mk, mv, p);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : 3;
 }
 

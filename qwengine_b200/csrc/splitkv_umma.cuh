@@ -15,6 +15,6 @@ void splitkv_umma_layout(int rb, int *q_rows_pad, int *nslot);
 // K map: box 64 x 128 rows; V map: box 64 x 32 rows.  p.rb / p.nblk / p.G / p.ws / p.cnt must be set
 // for 128-key tiles and splitkv_umma_rb().  Returns 0 or a QW_ERR_* code.
 int launch_splitkv_umma(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, bool out_is_f32,
-                        cudaStream_t st);
+                        cudaStream_t st, bool dependent);
 
 }  // namespace qwb

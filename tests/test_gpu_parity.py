@@ -311,3 +311,32 @@ def test_graph_capture_and_replay_advances_with_device_position():
         if p < 300:
             assert np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 4e-3
     assert not np.array_equal(outs[1], outs[2])
+
+
+def test_fused_mixer_step_in_a_cuda_graph():
+    """The two-launch decode step (append kernel, then the attention kernel launched as its programmatic
+    dependent) is capturable and a replay gives the bits of the eager call."""
+    c = Case(81, [900, 131, 4000], 1)
+    eager, lse_eager, kc_eager, _, _ = run_case(c, out_f32=True)
+    mx = api.Mixer(c.n_seq, 1)
+    q, k, v, gate = dev_bf16(c.q), dev_bf16(c.k), dev_bf16(c.v), dev_bf16(c.gate)
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    out = torch.zeros(c.n_seq, 1, 24, 256, dtype=torch.float32, device="cuda")
+    lse = torch.zeros(c.n_seq, 1, 24, dtype=torch.float32, device="cuda")
+    mx.bind(q, kc, vc, torch.from_numpy(c.hist).cuda(), out, k_new=k, v_new=v, gate=gate, lse=lse,
+            cache_row=torch.from_numpy(c.cache_row).cuda())
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        mx.forward(stream=s)  # warm-up: one-time kernel attributes are set outside the capture
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            mx.forward(stream=s)
+    out.zero_()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    mx.check_status()
+    assert np.array_equal(host_f32(out).reshape(-1, 24, 256), eager)
+    assert np.array_equal(lse.cpu().numpy().reshape(-1, 24), lse_eager)
+    assert np.array_equal(host_bits(kc), kc_eager)
