@@ -205,6 +205,9 @@ int launch_splitkv(const AttnCall &c, cudaStream_t st) {
   p.q_lo_dims = c.q_is_f32 ? HEAD_DIM : (c.do_rope ? ROTARY_DIM : 0);
   p.scale_log2 = c.scale * LOG2E;
   p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate; p.no_causal = c.no_causal; p.q_dep = c.q_dep;
+#ifdef QWB_TIMELINE
+  p.dbg = qwb::g_timeline_buf; p.dbg_block = qwb::g_timeline_block;
+#endif
   p.rope = make_rope_table(c.theta, ROTARY_DIM);
 
   CUtensorMap mk, mv;

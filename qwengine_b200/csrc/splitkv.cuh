@@ -302,6 +302,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
   const int cta = blockIdx.x;
+  if (tid == 0) { QWB_TLB(0); QWB_TL(30, 0); }
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], NCW); }
@@ -319,6 +320,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   __syncthreads();
   const long long total = seg[0];
   const int G = (int)(seg[2] >> 32);                  // CTAs in use (the rest of the grid leaves here)
+  if (tid == 0) QWB_TL(30, 1);
   const long long g0 = cta < G ? total * cta / G : 0, g1 = cta < G ? total * (cta + 1) / G : 0;
   if (g0 >= g1) return;  // uniform for the whole CTA
 
@@ -385,6 +387,8 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   uint32_t it = 0;
   int u = (int)(seg[2] & 0xffffffffll);
   long long pre = seg[1];
+  int segx = 0;  // segments done (timeline probe only)
+  (void)segx;
   const uint32_t qhi_s = smem_u32(qregion);
   // Per-lane ldmatrix addresses.  The swizzle XORs the 16-byte column (d / 8) & 7 with row & 7,
   // so for a fixed lane only four distinct column offsets occur; the rest is a constant stride.
@@ -416,18 +420,42 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     // ---- stage Q: rotate, split into bf16 hi (+ lo), zero the padding rows ----
     if (p.q_dep) grid_dep_wait();  // q comes out of the launch before this one
     consumer_sync(NCT);  // the previous segment is done with this region
-    for (int idx = tid; idx < ROWS * 32; idx += NCT) {
+    // All global loads of the staging are issued before the first one is used: one memory round trip
+    // for the segment instead of one per loop iteration.
+    constexpr int QIT = (ROWS * 32 + NCT - 1) / NCT;
+    float xq[QIT][8], rx[QIT], ry[QIT];
+#pragma unroll
+    for (int it = 0; it < QIT; ++it) {
+      const int idx = tid + it * NCT;
       const int row = idx >> 5, c16 = idx & 31;  // 8 channels d = c16*8 .. +7
-      if (p.do_rope && c16 < 8) continue;        // rotary channels are written pair-wise below
-      const int b = row / GROUP, hh = row % GROUP;
-      const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
-      float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (row < R) load8<TIn>(reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM + c16 * 8, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) xq[it][j] = 0.f;
+      if (idx < ROWS * 32 && row < R && !(p.do_rope && c16 < 8)) {
+        const int b = row / GROUP, hh = row % GROUP;
+        const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
+        load8<TIn>(reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM + c16 * 8, xq[it]);
+      }
+      rx[it] = ry[it] = 0.f;
+      if (p.do_rope && idx < ROWS * ROT_PAIRS) {
+        const int rrow = idx / ROT_PAIRS, i = idx % ROT_PAIRS;  // pair (i, i + 32) of this row
+        if (rrow < R) {
+          const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + rrow / GROUP) * p.q_heads + (size_t)ui.kvh * GROUP + rrow % GROUP;
+          const TIn *src = reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM;
+          rx[it] = load_as_f32<TIn>(src + i);
+          ry[it] = load_as_f32<TIn>(src + i + ROT_PAIRS);
+        }
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < QIT; ++it) {
+      const int idx = tid + it * NCT;
+      const int row = idx >> 5, c16 = idx & 31;
+      if (idx >= ROWS * 32 || (p.do_rope && c16 < 8)) continue;  // rotary channels are written pair-wise below
       uint32_t hi[4], lo[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        hi[j] = pack_bf16(x[2 * j], x[2 * j + 1]);
-        lo[j] = pack_bf16(x[2 * j] - bf16lo(hi[j]), x[2 * j + 1] - bf16hi(hi[j]));
+        hi[j] = pack_bf16(xq[it][2 * j], xq[it][2 * j + 1]);
+        lo[j] = pack_bf16(xq[it][2 * j] - bf16lo(hi[j]), xq[it][2 * j + 1] - bf16hi(hi[j]));
       }
       *reinterpret_cast<uint4 *>(qregion + q_hi_off(row, c16 * 8)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
       if (c16 * 8 < p.q_lo_dims)
@@ -435,20 +463,19 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
             make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
     if (p.do_rope) {
-      for (int idx = tid; idx < ROWS * ROT_PAIRS; idx += NCT) {
-        const int row = idx / ROT_PAIRS, i = idx % ROT_PAIRS;  // pair (i, i + 32) of this row
-        const int b = row / GROUP, hh = row % GROUP;
+#pragma unroll
+      for (int it = 0; it < QIT; ++it) {
+        const int idx = tid + it * NCT;
+        if (idx >= ROWS * ROT_PAIRS) continue;
+        const int row = idx / ROT_PAIRS, i = idx % ROT_PAIRS;
         float xr = 0.f, yr = 0.f;
         if (row < R) {
-          const size_t trow = (size_t)ui.s * p.n_new + ui.tok0 + b;
-          const size_t grow = trow * p.q_heads + (size_t)ui.kvh * GROUP + hh;
-          const TIn *src = reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM;
-          const float x = load_as_f32<TIn>(src + i), y = load_as_f32<TIn>(src + i + ROT_PAIRS);
-          const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.pos + ui.tok0 + b;
+          const size_t trow = (size_t)ui.s * p.n_new + ui.tok0 + row / GROUP;
+          const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.pos + ui.tok0 + row / GROUP;
           float c, sn;
           rope_sincos_reduced(pz, p.rope.inv_freq[i], c, sn);  // angle reduced in double, then the fast sincos
-          xr = x * c - y * sn;
-          yr = x * sn + y * c;
+          xr = rx[it] * c - ry[it] * sn;
+          yr = rx[it] * sn + ry[it] * c;
         }
         const uint16_t xh = f32_to_bf16_bits(xr), yh = f32_to_bf16_bits(yr);
         *reinterpret_cast<uint16_t *>(qregion + q_hi_off(row, i)) = xh;
@@ -462,6 +489,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       }
     }
     consumer_sync(NCT);
+    if (tid == 0) QWB_TL(30, 2 + 8 * segx);
     uint32_t qf[QREG ? 16 : 1][4], qlf[QREG && LOK > 0 ? LOK : 1][4];
     if (QREG) {
 #pragma unroll
@@ -627,6 +655,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       if (lane == 0) mbar_arrive(&empty[st]);
     }
 
+    if (tid == 0) QWB_TL(30, 9 + 8 * segx);
     // ---- merge the SK_KS key-slice warps of each channel group, in slice order ----
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -642,6 +671,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         }
       }
     consumer_sync(NCT);  // also: every warp is past its last tile, the Q area may be reused
+    if (tid == 0) QWB_TL(30, 3 + 8 * segx);
     float *comb = reinterpret_cast<float *>(qregion);  // [ROWS][256] fp32, 8-float groups XOR (row & 7)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -656,8 +686,26 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
 #pragma unroll
         for (int n = 0; n < NT_O; ++n) { o[mt][n][2 * h2] *= f; o[mt][n][2 * h2 + 1] *= f; }
       }
+    if (tid == 0) QWB_TL(30, 7 + 8 * segx);
     for (int k = 0; k < SK_KS; ++k) {
       if (ks == k) {
+        // all loads of the round first, then all stores: read-add-write per element would serialise on
+        // shared-memory latency (32 dependent round trips per thread and round)
+        if (k) {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int row = mt * 16 + h2 * 8 + qd;
+#pragma unroll
+              for (int n = 0; n < NT_O; ++n) {
+                const int d = ds * DW + n * 8 + ql * 2;
+                const float2 w = *reinterpret_cast<const float2 *>(comb + row * HEAD_DIM + (d ^ ((row & 7) << 3)));
+                o[mt][n][2 * h2] += w.x;
+                o[mt][n][2 * h2 + 1] += w.y;
+              }
+            }
+        }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -666,16 +714,15 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
 #pragma unroll
             for (int n = 0; n < NT_O; ++n) {
               const int d = ds * DW + n * 8 + ql * 2;
-              float2 *dst = reinterpret_cast<float2 *>(comb + row * HEAD_DIM + (d ^ ((row & 7) << 3)));
-              float2 v = make_float2(o[mt][n][2 * h2], o[mt][n][2 * h2 + 1]);
-              if (k) { const float2 w = *dst; v.x += w.x; v.y += w.y; }
-              *dst = v;
+              *reinterpret_cast<float2 *>(comb + row * HEAD_DIM + (d ^ ((row & 7) << 3))) =
+                  make_float2(o[mt][n][2 * h2], o[mt][n][2 * h2 + 1]);
             }
           }
       }
       consumer_sync(NCT);
     }
 
+    if (tid == 0) QWB_TL(30, 8 + 8 * segx);
     // ---- finish the segment: final output, or a partial for the merge kernel ----
     for (int idx = tid; idx < R * 32; idx += NCT) {
       const int row = idx >> 5, c8 = idx & 31;  // channels c8*8 .. +7
@@ -716,6 +763,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         if (c8 == 0) { dst[256] = mg; dst[257] = lg; }
       }
     }
+    if (tid == 0) QWB_TL(30, 4 + 8 * segx);
     // ---- with arrival counters: the CTA that completes a unit last merges it right here ----
     if (!whole && p.cnt) {
       __threadfence();  // this thread's partial stores are visible device-wide before the ticket
@@ -725,6 +773,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         *ticket = atomicAdd(&p.cnt[u], 1);
       }
       consumer_sync(NCT);
+      if (tid == 0) QWB_TL(30, 5 + 8 * segx);
       const int c_first = cta_of_tile(pre, total, G), c_last = cta_of_tile(pre + nt_unit - 1, total, G);
       int nparts = 0;
       for (int c = c_first; c <= c_last; ++c) nparts += (total * c / G != total * (c + 1) / G) ? 1 : 0;
@@ -734,9 +783,12 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         if (tid == 0) p.cnt[u] = 0;  // leave the counter clean for a caller that does not reset it
       }
     }
+    if (tid == 0) QWB_TL(30, 6 + 8 * segx);
+    ++segx;
     pre += nt_unit;
     ++u;
   }
+  if (tid == 0) QWB_TLB(1);
 }
 
 // Merge the partials of every unit that was cut across CTAs.  One block per unit, one warp per

@@ -12,17 +12,7 @@ constexpr uint32_t TMEM_O = 0, TMEM_S0 = 256, TMEM_S1 = 384;
 
 // Timeline probe for kernel bring-up: with -DQWB_TIMELINE one CTA records clock64() at named
 // events into a caller-supplied buffer [event][tile]; compiled out otherwise.
-#ifdef QWB_TIMELINE
-#define QWB_TL(ev, j) do { if (p.dbg && (int)blockIdx.x == p.dbg_block && (j) < 64) p.dbg[(ev) * 64 + (j)] = ((ev) == 30 || (ev) == 31) ? global_timer_ns() : (unsigned long long)clock64(); } while (0)
-#define QWB_TLB(k) do { if (p.dbg && p.dbg_block < 0) p.dbg[2048 + 2 * blockIdx.x + (k)] = global_timer_ns(); } while (0)
-#define QWB_TLV(ev, j, val) do { if (p.dbg && (int)blockIdx.x == p.dbg_block && (j) < 64) p.dbg[(ev) * 64 + (j)] = (unsigned long long)(val); } while (0)
-extern unsigned long long *g_timeline_buf;
-extern int g_timeline_block;
-#else
-#define QWB_TL(ev, j) do { } while (0)
-#define QWB_TLV(ev, j, val) do { } while (0)
-#define QWB_TLB(k) do { } while (0)
-#endif
+
 
 struct PrefillParams {
   const uint16_t *gate;
