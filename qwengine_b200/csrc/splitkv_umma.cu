@@ -100,11 +100,12 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   if (warp == 2) {
     long long total; int live, geff; bool aligned;
     warp_partition<DU_BN>(p, n_units, lane, total, live, geff, aligned);
-    const int lead = aligned ? 0 : min(DU_SWITCH_TILES + (p.rb * GROUP) / 4, 3 * DU_SWITCH_TILES);
-    // Where the grid could not be aligned with the units, a CTA whose slice runs over a unit
-    // boundary loses several tiles of time there (the pipeline drains: last P V, read-out of O, new
-    // Q tile; 4 tiles measured with 6 rows, 9 with 24).  The flat list charges for it: every unit is
-    // preceded by `lead` entries that stand for no tile, so such a CTA receives that many tiles less.
+    const int lead = aligned ? 0 : DU_SWITCH_TILES + (p.rb * GROUP) / 16;
+    // Where the grid could not be aligned with the units, a CTA whose slice runs over a unit boundary
+    // loses time there (the pipeline drains: last P V, read-out of O, new Q tile): about 11 us, three
+    // to four tiles, measured.  The flat list charges for it: every unit is preceded by `lead` entries
+    // that stand for no tile, so such a CTA receives that many tiles less.  Weights of 4 to 6 tiles
+    // time the same within 1 %; 0 and 10 are 3 % slower.
     total += (long long)lead * live;
     int u0 = n_units; long long pre0 = 0;
     if (cta < geff) warp_find_unit<DU_BN>(p, n_units, lane, total * cta / geff, u0, pre0, lead);
