@@ -296,7 +296,7 @@ def hbm_line(name, r, world, peaks):
                    "l2_policy": "inputs larger than L2: %.0f MB of KV per GPU per step vs 126 MB L2" % (w["kv_bytes"] / 1e6)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
                      "frac": round(achieved / hbm_peak, 4),
-                     "traffic": ({"decode": 546.2e6, "verify": 690.8e6}[name] if world == 1 else None),
+                     "traffic": ({"decode": 545.4e6, "verify": 689.2e6}[name] if world == 1 else None),
                      "traffic_source": "ncu dram read+write bytes per launch, profiles/%s.txt"
                                        % ("splitkv_decode_config2" if name == "decode" else "splitkv_umma_verify"),
                      "algorithmic_bytes": w["kv_bytes"], "peak_kind": kind,
