@@ -193,18 +193,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 __device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// Untiled bulk copy global -> shared::cta, completion counted on an mbarrier.  Both addresses 16-byte
-// aligned, size a multiple of 16 bytes.
-__device__ __forceinline__ void bulk_load(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-// 16-byte asynchronous copy global -> shared (no registers held while in flight) and its wait.
-__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

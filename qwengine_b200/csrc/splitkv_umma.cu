@@ -46,8 +46,6 @@ struct DecCtl {
   volatile int merge_go;
   volatile int merge_parts[2];   // CTAs that hold a part of each pending unit
   volatile uint8_t merge_live[2][DU_MAX_PARTS];
-  uint16_t merge_list[DU_MAX_PARTS];  // offsets (from c_first) of the CTAs that hold a part of the unit being merged
-  uint64_t merge_bar;                 // completion of the bulk copies of a merge
   long long part[5];             // total tiles, flat index of the first unit's tile 0, first unit, CTAs in use, lead entries per unit
   float mxbuf[2][DU_NWG][128];
   float lbuf[DU_NWG][128];
@@ -91,7 +89,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       mbar_init(&ctl->o_done[i], 1);
     }
     for (int i = 0; i < DU_MAX_SLOT; ++i) { mbar_init(&ctl->slot_full[i], 1); mbar_init(&ctl->slot_empty[i], 1); }
-    mbar_init(&ctl->merge_bar, 1);
     ctl->abort_flag = (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) ? 1 : 0;
     fence_barrier_init();
     prefetch_tensormap(&mapK);
@@ -355,7 +352,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     };
     // units cut across CTAs: their merge is settled after this CTA's last tile
     int pend_u[2] = {0, 0}, pend_nt[2] = {0, 0}, n_pend = 0;
-    uint32_t merge_phase = 0;
     long long pend_pre[2] = {0, 0};
     if (tid == 64) QWB_TL(30, 3);
     int nt, t0, t1;
@@ -586,64 +582,10 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           if (tid == 64) QWB_TL(30, 54 + 3 * k);
           const int c_first = cta_of_tile(pend_pre[k] + LEAD, total, G), c_last = cta_of_tile(pend_pre[k] + LEAD + pend_nt[k] - 1, total, G);
           const UnitInfo ui = unit_info(p, pend_u[k]);
-          const int R = ui.ntok * GROUP, span = c_last - c_first + 1, P = ctl->merge_parts[k];
-          constexpr int ROW_BYTES = PART_STRIDE * 4, ROW_CHUNKS = ROW_BYTES / 16;
-          const int cap_rows = (DU_SMEM_TOTAL - (int)sizeof(DecCtl)) / ROW_BYTES;  // part rows that fit in shared memory
-          if (span <= DU_MAX_PARTS && P >= 1 && P <= cap_rows) {
-            // The parts of a group of rows are fetched into the (now idle) Q / ring area by bulk copies
-            // (a part's rows are contiguous in its slot), all in flight at once: one memory round trip
-            // per group instead of one per four parts.  Then a warp folds each row, in CTA order.
-            const int rows_per = min(R, cap_rows / P);
-            if (st_tid == 0) {  // compact list of the CTAs that hold a part
-              int n = 0;
-              for (int i = 0; i < span; ++i)
-                if (ctl->merge_live[k][i]) ctl->merge_list[n++] = (uint16_t)i;
-            }
-            bool mok = true;
-            for (int r0 = 0; r0 < R; r0 += rows_per) {
-              const int nr = min(rows_per, R - r0);
-              asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");  // list written / previous group folded
-              if (st_tid == 0) {
-                fence_proxy_async();
-                mbar_expect_tx(&ctl->merge_bar, (uint32_t)(P * nr * ROW_BYTES));
-                for (int j = 0; j < P; ++j) {
-                  const float *src = p.ws + ((size_t)(c_first + ctl->merge_list[j] + pend_u[k]) * (p.rb * GROUP) + r0) * PART_STRIDE;
-                  bulk_load(smem + (size_t)j * rows_per * ROW_BYTES, src, (uint32_t)(nr * ROW_BYTES), &ctl->merge_bar);
-                }
-              }
-              if (mok) mok = wait_or_abort(&ctl->merge_bar, merge_phase & 1, abort_flag);
-              ++merge_phase;
-              if (!mok) {
-                if (st_tid == 0) fail(DEV_ERR_SOFTMAX_WAIT);
-                continue;
-              }
-              for (int rr = warp - 2; rr < nr; rr += DU_NWG * 4) {
-                float mg = -INFINITY, lg = 0.f;
-                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                for (int j = 0; j < P; ++j) {
-                  const float *src = reinterpret_cast<const float *>(smem + ((size_t)j * rows_per + rr) * ROW_BYTES);
-                  const float mv = src[256], lv = src[257];
-                  if (!(lv > 0.f)) continue;
-                  const float4 av = *reinterpret_cast<const float4 *>(src + lane * 8);
-                  const float4 bv = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
-                  const float m_new = fmaxf(mg, mv);
-                  const float f_old = fast_exp2(mg - m_new), f = fast_exp2(mv - m_new);  // mg = -inf gives f_old = 0
-                  mg = m_new;
-                  lg = lg * f_old + lv * f;
-                  acc[0] = acc[0] * f_old + av.x * f; acc[1] = acc[1] * f_old + av.y * f;
-                  acc[2] = acc[2] * f_old + av.z * f; acc[3] = acc[3] * f_old + av.w * f;
-                  acc[4] = acc[4] * f_old + bv.x * f; acc[5] = acc[5] * f_old + bv.y * f;
-                  acc[6] = acc[6] * f_old + bv.z * f; acc[7] = acc[7] * f_old + bv.w * f;
-                }
-                merge_finish<TOut>(p, ui, r0 + rr, lane, mg, lg, acc);
-              }
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");  // before the next unit reuses the area
-          } else {
-            for (int r = warp - 2; r < R; r += DU_NWG * 4)
-              merge_unit_row<TOut>(p, pend_u[k], ui, r, c_first, c_last, total, lane, G,
-                                   span <= DU_MAX_PARTS ? ctl->merge_live[k] : nullptr);
-          }
+          const int R = ui.ntok * GROUP, span = c_last - c_first + 1;
+          for (int r = warp - 2; r < R; r += DU_NWG * 4)
+            merge_unit_row<TOut>(p, pend_u[k], ui, r, c_first, c_last, total, lane, G,
+                                 span <= DU_MAX_PARTS ? ctl->merge_live[k] : nullptr);
           if (st_tid == 0) p.cnt[pend_u[k]] = 0;
           if (tid == 64) QWB_TL(30, 55 + 3 * k);
         }
