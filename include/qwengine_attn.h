@@ -233,6 +233,18 @@ int qw_mixer_forward_partial(const qw_mixer_desc *d, float *partial, qw_stream s
 int qw_combine_partials(const float *parts, int n_parts, int64_t rows, int q_heads,
                         const qw_bf16 *gate, void *out, float *lse, int flags, qw_stream stream);
 
+/* The same merge with the exchange done inside the kernel over NVLink peer memory instead of a collective in
+ * front of it.  part_ptrs / flag_ptrs: device arrays of n_parts pointers, element k being THIS process's
+ * mapping of rank k's partial buffer [rows][q_heads][260] and of rank k's flag word (symmetric memory, CUDA IPC
+ * or any other peer mapping; the flag words start at zero).  Every rank calls it with the same `step`
+ * (1, 2, 3, ...) after the launch that wrote its own partials on the same stream; the kernel publishes the step
+ * in the rank's own flag, waits (at most two seconds, else *status = 106 and the output is left alone) until
+ * every peer has published it, then reads the peers' partials in place.  Alternate two buffer / flag sets by
+ * step parity.  No counterpart in the reference (single GPU). */
+int qw_combine_partials_peer(const float *const *part_ptrs, int *const *flag_ptrs, int rank, int n_parts, int step,
+                             int64_t rows, int q_heads, const qw_bf16 *gate, void *out, float *lse, int flags,
+                             int *status, qw_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,6 +61,7 @@ _SIGS = {
     "qw_mixer_forward_partial": (_i, [C.POINTER(MixerDesc), _vp, _vp]),
     "qw_mixer_forward_fused": (_i, [C.POINTER(MixerDesc), _vp, _i, _vp, _vp, _f, _vp]),
     "qw_combine_partials": (_i, [_vp, _i, C.c_int64, _i, _vp, _vp, _vp, _i, _vp]),
+    "qw_combine_partials_peer": (_i, [_vp, _vp, _i, _i, _i, C.c_int64, _i, _vp, _vp, _vp, _i, _vp, _vp]),
 }
 
 _lib = None
@@ -220,6 +221,15 @@ def profile_last_kernel_ms():
 
 def _addr(t):
     return None if t is None else t.data_ptr()
+
+
+def combine_partials_peer(part_ptrs, flag_ptrs, rank, n_parts, step, rows, q_heads, out, gate=None, lse=None, status=None,
+                          stream=None):
+    """Merge with the exchange inside the kernel: part_ptrs / flag_ptrs are int64 CUDA tensors holding this
+    process's mappings of every rank's partial buffer and flag word (see qwengine_b200.sharding.PeerExchange)."""
+    flags = (F_GATE if gate is not None else 0) | (F_OUT_F32 if out.dtype == torch.float32 else 0)
+    _check(lib().qw_combine_partials_peer(_p(part_ptrs), _p(flag_ptrs), rank, n_parts, step, rows, q_heads, _p(gate),
+                                          _p(out), _p(lse), flags, _p(status), _stream(stream)))
 
 
 def combine_partials(parts, n_parts, rows, q_heads, out, gate=None, lse=None, stream=None):

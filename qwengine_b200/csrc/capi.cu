@@ -664,4 +664,25 @@ int qw_combine_partials(const float *parts, int n_parts, int64_t rows, int q_hea
   return check_launch("combine_partials_kernel");
 }
 
+int qw_combine_partials_peer(const float *const *part_ptrs, int *const *flag_ptrs, int rank, int n_parts, int step,
+                             int64_t rows, int q_heads, const qw_bf16 *gate, void *out, float *lse, int flags, int *status,
+                             qw_stream stream) {
+  g_launches = 0;
+  if (!part_ptrs || !flag_ptrs || !out || n_parts <= 0 || rank < 0 || rank >= n_parts || rows < 0 || q_heads <= 0 || step <= 0)
+    return QW_ERR_ARG;
+  if ((flags & QW_F_GATE) && !gate) return QW_ERR_ARG;
+  if (rows == 0) return QW_OK;
+  const long long n = (long long)rows * q_heads;
+  const unsigned blocks = (unsigned)((n + 7) / 8);
+  if (flags & QW_F_OUT_F32)
+    combine_partials_peer_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        part_ptrs, flag_ptrs, rank, n_parts, step, n, (flags & QW_F_GATE) ? gate : nullptr, reinterpret_cast<float *>(out),
+        lse, status);
+  else
+    combine_partials_peer_kernel<uint16_t><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        part_ptrs, flag_ptrs, rank, n_parts, step, n, (flags & QW_F_GATE) ? gate : nullptr,
+        reinterpret_cast<uint16_t *>(out), lse, status);
+  return check_launch("combine_partials_peer_kernel");
+}
+
 }  // extern "C"

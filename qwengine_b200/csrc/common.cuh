@@ -25,6 +25,7 @@ constexpr int DEV_ERR_EMPTY_WAIT = 102;  // producer waited too long for a free 
 constexpr int DEV_ERR_MMA_WAIT = 103;    // a wait on tcgen05 completion ran out
 constexpr int DEV_ERR_SOFTMAX_WAIT = 104;
 constexpr int DEV_ERR_TMEM = 105;
+constexpr int DEV_ERR_PEER_WAIT = 106;   // another GPU's partials did not show up in time
 
 struct RopeTable {
   double inv_freq[ROT_PAIRS];  // theta^(-2i/rot), computed on the host in double

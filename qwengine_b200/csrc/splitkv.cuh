@@ -857,6 +857,79 @@ __global__ void __launch_bounds__(256) combine_partials_kernel(const float *part
   if (lane == 0 && lse) lse[r] = (mg + log2f(lg)) * LN2;
 }
 
+// The same merge with the exchange inside the kernel, over NVLink peer memory: rank k's partials are read
+// straight from rank k's buffer (part_ptrs[k], a peer mapping of symmetric memory) -- no collective, no
+// staging copy.  Every block publishes this rank's step number in its own flag word (release, system scope;
+// the kernel that produced the partials ran before this one on the stream) and waits until every peer's flag
+// has reached the step (acquire, system scope).  The wait is bounded (PEER_WAIT_NS): on expiry the block
+// writes DEV_ERR_PEER_WAIT to *status and leaves without touching the output.  Buffers and flags alternate
+// by step parity, which is enough to keep a fast rank from overwriting what a slow one still reads: a rank
+// can publish step s + 2 only after its own combine of step s + 1, which waited for every peer to have
+// finished step s.
+constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;
+template <typename TOut>
+__global__ void __launch_bounds__(256) combine_partials_peer_kernel(const float *const *part_ptrs, int *const *flag_ptrs,
+                                                                    int rank, int n_parts, int step, long long n,
+                                                                    const uint16_t *gate, TOut *out, float *lse,
+                                                                    int *status) {
+  __shared__ int failed;
+  if (threadIdx.x == 0) {
+    failed = 0;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag_ptrs[rank]), "r"(step) : "memory");
+    const uint64_t t0 = global_timer_ns();
+    for (int k = 0; k < n_parts && !failed; ++k) {
+      if (k == rank) continue;
+      const int *f = flag_ptrs[k];
+      for (;;) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        if (v - step >= 0) break;  // the peer is at this step (or already past it)
+        if (global_timer_ns() - t0 > PEER_WAIT_NS) {
+          failed = 1;
+          if (status) *status = DEV_ERR_PEER_WAIT;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (failed) return;
+  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= n) return;
+  float mg = -INFINITY;
+  for (int k = 0; k < n_parts; ++k) {
+    const float *src = part_ptrs[k] + (size_t)r * PART_STRIDE;
+    if (src[257] > 0.f) mg = fmaxf(mg, src[256]);
+  }
+  const float m_use = (mg == -INFINITY) ? 0.f : mg;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float lg = 0.f;
+  for (int k = 0; k < n_parts; ++k) {  // rank order, as in combine_partials_kernel: same bits
+    const float *src = part_ptrs[k] + (size_t)r * PART_STRIDE;
+    const float l = src[257];
+    if (!(l > 0.f)) continue;
+    const float f = fast_exp2(src[256] - m_use);
+    lg += l * f;
+    const float4 a = *reinterpret_cast<const float4 *>(src + lane * 8);
+    const float4 b = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
+    acc[0] += a.x * f; acc[1] += a.y * f; acc[2] += a.z * f; acc[3] += a.w * f;
+    acc[4] += b.x * f; acc[5] += b.y * f; acc[6] += b.z * f; acc[7] += b.w * f;
+  }
+  const float inv = 1.f / lg;
+  if (gate) {
+    float g[8];
+    load8<uint16_t>(gate + r * HEAD_DIM + lane * 8, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv * sigmoidf_(g[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv;
+  }
+  store8<TOut>(out + r * HEAD_DIM + lane * 8, acc);
+  if (lane == 0 && lse) lse[r] = (mg + log2f(lg)) * LN2;
+}
+
 template <int MT, int DS, int STAGES>
 constexpr size_t splitkv_smem_bytes() {
   return 1024 + (size_t)STAGES * SK_STAGE_BYTES + (size_t)MT * 16 * 1024 + 2 * SK_KS * MT * 16 * 4 +

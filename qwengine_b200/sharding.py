@@ -83,3 +83,56 @@ def merge_partials_reference(parts):
         lg = lg + l[k] * f[k]
         acc = acc + o[k] * f[k][..., None]
     return acc / lg[..., None], (mg + torch.log2(lg)) * 0.6931471805599453
+
+
+class PeerExchange:
+    """Cross-GPU merge of split-KV partials without a collective: every rank writes its partials into a buffer
+    that its peers have mapped (torch symmetric memory over NVLink) and the combine kernel of each rank reads
+    the others' partials in place, after a flag handshake inside the kernel (qw_combine_partials_peer).
+    Two buffer / flag sets alternate by step so that a fast rank never overwrites what a slow one still reads.
+
+        ex = PeerExchange(rows, q_heads)             # collective: call on every rank of the group
+        mixer.forward_partial(ex.partial())          # this rank's (o, m, l) for its KV sub-range
+        ex.combine(out, gate=gate, lse=lse)          # merged, normalised, gated output
+    """
+
+    def __init__(self, rows, q_heads, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm
+        from . import api
+        self._api = api
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.rows, self.q_heads = rows, q_heads
+        self.n = rows * q_heads * api.PARTIAL_FLOATS
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        # [two partial buffers | 64 ints of flags]; float32 storage, the flags are viewed as int32
+        self.buf = symm.empty(2 * self.n + 64, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        hdl = symm.rendezvous(self.buf, group)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                          # every flag word is zero before anyone publishes a step
+        self._hdl = hdl
+        self.part_ptrs = [torch.tensor([p + par * self.n * 4 for p in ptrs], dtype=torch.int64, device=device)
+                          for par in (0, 1)]
+        self.flag_ptrs = [torch.tensor([p + (2 * self.n + par) * 4 for p in ptrs], dtype=torch.int64, device=device)
+                          for par in (0, 1)]
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.step = 0
+
+    def partial(self):
+        """This rank's partial buffer for the NEXT combine: [rows, q_heads, 260] float32 (a view, no copy)."""
+        par = (self.step + 1) & 1
+        return self.buf[par * self.n:(par + 1) * self.n].view(self.rows, self.q_heads, self._api.PARTIAL_FLOATS)
+
+    def combine(self, out, gate=None, lse=None, stream=None):
+        self.step += 1
+        par = self.step & 1
+        self._api.combine_partials_peer(self.part_ptrs[par], self.flag_ptrs[par], self.rank, self.world, self.step,
+                                        self.rows, self.q_heads, out, gate=gate, lse=lse, status=self.status,
+                                        stream=stream)
+
+    def check_status(self):
+        code = int(self.status.item())
+        if code:
+            raise RuntimeError("peer combine reported device error code %d" % code)

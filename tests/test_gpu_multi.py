@@ -1,7 +1,8 @@
 """Split of one sequence's KV range across ranks: each rank attends to its sub-range and emits
 (o, m, l) partials, the partials are gathered and merged in rank order.  On one GPU the two
 sub-ranges are run one after the other (same kernels, same merge); with two or more GPUs the
-exchange is a real NCCL all-gather between processes."""
+exchange is a real NCCL all-gather between processes, and also the peer-memory merge that needs no
+collective (sharding.PeerExchange)."""
 import os
 import socket
 
@@ -88,7 +89,18 @@ def _nccl_worker(rank, world, port, hist, B, ret):
         torch.cuda.synchronize()
         from tests.util import rel_l2
         got = host_f32(out)
-        ret[rank] = bool(np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 3e-3)
+        ok = bool(np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 3e-3)
+        # the same merge with the exchange inside the kernel, over peer memory: three steps in a row (both buffer
+        # sets, and the first one again), each bit-identical to the all-gather + combine result
+        ex = sharding.PeerExchange(B, c.q_heads)
+        for _ in range(3):
+            ex.partial().copy_(part)
+            out2 = torch.zeros(B, c.q_heads, 256, dtype=torch.float32, device="cuda")
+            ex.combine(out2, gate=dev_bf16(c.gate[0]))
+            torch.cuda.synchronize()
+            ex.check_status()
+            ok = ok and bool(np.array_equal(host_f32(out2), got))
+        ret[rank] = ok
     finally:
         torch.distributed.destroy_process_group()
 
@@ -102,3 +114,27 @@ def test_kv_range_split_across_two_gpus_with_nccl():
     ret = mp.Manager().dict()
     mp.spawn(_nccl_worker, args=(2, port, 2500, 4, ret), nprocs=2, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+def test_peer_combine_gives_up_when_a_peer_never_publishes():
+    """Failure detection without a fault: rank 1's flag word is never set, so the bounded wait in the kernel runs
+    out, the status word receives the device error code and the output is left untouched; the context stays usable."""
+    rows, heads = 2, 24
+    parts = torch.zeros(2, rows, heads, api.PARTIAL_FLOATS, dtype=torch.float32, device="cuda")
+    parts[..., 257] = 1.0
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    part_ptrs = torch.tensor([parts[0].data_ptr(), parts[1].data_ptr()], dtype=torch.int64, device="cuda")
+    flag_ptrs = torch.tensor([flags[0:1].data_ptr(), flags[1:2].data_ptr()], dtype=torch.int64, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.full((rows, heads, 256), 7.0, dtype=torch.float32, device="cuda")
+    api.combine_partials_peer(part_ptrs, flag_ptrs, 0, 2, 1, rows, heads, out, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 106
+    assert int(flags[0].item()) == 1 and int(flags[1].item()) == 0
+    assert bool((out == 7.0).all())
+    # once the "peer" has published, the same call goes through
+    flags[1] = 1
+    status.zero_()
+    api.combine_partials_peer(part_ptrs, flag_ptrs, 0, 2, 1, rows, heads, out, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and bool((out == 0.0).all())
