@@ -766,11 +766,15 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     if (tid == 0) QWB_TL(30, 4 + 8 * segx);
     // ---- with arrival counters: the CTA that completes a unit last merges it right here ----
     if (!whole && p.cnt) {
-      __threadfence();  // this thread's partial stores are visible device-wide before the ticket
+      // Release: the barrier orders every thread's partial stores before thread 0's fence, which is cumulative,
+      // so one fence + atomic publishes the whole CTA's partial.  Acquire: the fence after the atomic, then the
+      // barrier, order the merge's loads (which bypass L1) after the other CTAs' tickets.
       consumer_sync(NCT);
       if (tid == 0) {
+        __threadfence();
         grid_dep_wait();  // the append kernel of this step clears the counters
         *ticket = atomicAdd(&p.cnt[u], 1);
+        __threadfence();
       }
       consumer_sync(NCT);
       if (tid == 0) QWB_TL(30, 5 + 8 * segx);
@@ -778,7 +782,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       int nparts = 0;
       for (int c = c_first; c <= c_last; ++c) nparts += (total * c / G != total * (c + 1) / G) ? 1 : 0;
       if (*ticket == nparts - 1) {
-        __threadfence();
         for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, G);
         if (tid == 0) p.cnt[u] = 0;  // leave the counter clean for a caller that does not reset it
       }

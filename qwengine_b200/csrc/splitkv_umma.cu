@@ -557,11 +557,14 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         for (int i = st_tid; i <= c_last - c_first && i < DU_MAX_PARTS; i += DU_SM_THREADS)
           ctl->merge_live[k][i] = (total * (c_first + i) / G != total * (c_first + i + 1) / G) ? 1 : 0;
       }
-      __threadfence();
+      // release / acquire through one thread: the barrier orders every thread's partial stores before that
+      // thread's (cumulative) fence and ticket; its second fence and the next barrier order the merge's loads
+      // (which bypass L1) after the other CTAs' tickets
       asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
       if (tid == 64) QWB_TL(30, 51);
       if (st_tid == 0) {  // one thread decides, so that a failure flagged meanwhile cannot split the group
         const int go = *abort_flag ? 0 : 1;
+        __threadfence();
         grid_dep_wait();  // the append kernel of this step clears the counters
         for (int k = 0; k < n_pend && go; ++k) {
           const int c_first = cta_of_tile(pend_pre[k] + LEAD, total, G), c_last = cta_of_tile(pend_pre[k] + LEAD + pend_nt[k] - 1, total, G);
@@ -571,6 +574,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           ctl->merge_parts[k] = nparts;
           ctl->ticket[k] = atomicAdd(&p.cnt[pend_u[k]], 1);
         }
+        __threadfence();
         ctl->merge_go = go;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
@@ -578,7 +582,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       for (int k = 0; k < n_pend && ctl->merge_go; ++k) {
         if (tid == 64) { QWB_TL(30, 53 + 3 * k); QWB_TLV(29, k, ctl->merge_parts[k] * 1000 + ctl->ticket[k]); }
         if (ctl->ticket[k] == ctl->merge_parts[k] - 1) {
-          __threadfence();
           if (tid == 64) QWB_TL(30, 54 + 3 * k);
           const int c_first = cta_of_tile(pend_pre[k] + LEAD, total, G), c_last = cta_of_tile(pend_pre[k] + LEAD + pend_nt[k] - 1, total, G);
           const UnitInfo ui = unit_info(p, pend_u[k]);
