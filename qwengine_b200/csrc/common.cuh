@@ -97,6 +97,14 @@ __device__ __forceinline__ long long cache_row_of(const PageMap &pm, const int64
   const int pg = t / pm.page_rows;
   return (long long)pm.table[(size_t)s * pm.stride + pg] * pm.page_rows + (t - pg * pm.page_rows);
 }
+// The same for a producer loop: `base` is the sequence's first row, read once (cache_row[s], or 0); only the
+// paged layout costs a memory access per call.  Loads issued while an SM streams K/V through TMA are slow,
+// so a producer must not repeat them per copy.
+__device__ __forceinline__ long long cache_row_at(const PageMap &pm, long long base, int s, int t) {
+  if (!pm.table) return base + t;
+  const int pg = t / pm.page_rows;
+  return (long long)pm.table[(size_t)s * pm.stride + pg] * pm.page_rows + (t - pg * pm.page_rows);
+}
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
 // Same value to ~2 ulp with the approximate reciprocal: for epilogues that are instruction-bound.

@@ -78,6 +78,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   const int qt = p.n_qtiles - 1 - rem / p.q_heads;
   const int head = rem % p.q_heads;
   const int kvh = head / GROUP;
+  const long long crow = p.cache_row ? p.cache_row[s] : 0;  // first cache row of the sequence (contiguous layout)
   const int q0 = qt * PF_BM;
   const int rows_valid = min(PF_BM, p.n_new - q0);
   const int pos = p.pos[s];
@@ -133,7 +134,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
             break;
           }
           mbar_expect_tx(&ctl->slot_full[sl], PF_SLOT);
-          tma_load_2d(ring + sl * PF_SLOT, &mapK, &ctl->slot_full[sl], kvh * HEAD_DIM + c * 64, (int)cache_row_of(p.pages, p.cache_row, s, j * PF_BN));
+          tma_load_2d(ring + sl * PF_SLOT, &mapK, &ctl->slot_full[sl], kvh * HEAD_DIM + c * 64, (int)cache_row_at(p.pages, crow, s, j * PF_BN));
         }
       };
       auto load_v = [&](int j) {
@@ -149,7 +150,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 #pragma unroll
           for (int c = 0; c < 4; ++c)  // 32 keys x 64 channels each, channel atoms 4 KB apart
             tma_load_2d(ring + sl * PF_SLOT + c * 4096, &mapV, &ctl->slot_full[sl], kvh * HEAD_DIM + c * 64,
-                        (int)cache_row_of(p.pages, p.cache_row, s, j * PF_BN + g * 32));
+                        (int)cache_row_at(p.pages, crow, s, j * PF_BN + g * 32));
         }
       };
       for (int j = 0; j <= nt && ok; ++j) {

@@ -169,6 +169,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
   const int qt = p.n_qtiles - 1 - rem / (p.q_heads / 2);
   const int head = (rem % (p.q_heads / 2)) * 2 + (int)rank;
   const int kvh = head / GROUP;
+  const long long crow = p.cache_row ? p.cache_row[s] : 0;  // first cache row of the sequence (contiguous layout)
   const int q0 = qt * P2_BM;
   const int rows_valid = min(P2_BM, p.n_new - q0);
   const int pos = p.pos[s];
@@ -245,7 +246,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
             }
             const uint32_t bar = map_to_cta(smem_u32(&ctl->slot_full[sl]), 0);
             remote_arrive_expect_tx(bar, P2_SLOT);
-            const int krow = (int)cache_row_of(p.pages, p.cache_row, s, j * P2_BN + (int)rank * 64);
+            const int krow = (int)cache_row_at(p.pages, crow, s, j * P2_BN + (int)rank * 64);
 #pragma unroll
             for (int a = 0; a < 2; ++a)
               tma_load_2d_pair(ring + sl * P2_SLOT + a * 8192, &mapK, bar, kvh * HEAD_DIM + (2 * i + a) * 64, krow);
@@ -262,7 +263,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
             }
             const uint32_t bar = map_to_cta(smem_u32(&ctl->slot_full[sl]), 0);
             remote_arrive_expect_tx(bar, P2_SLOT);
-            const int vrow = (int)cache_row_of(p.pages, p.cache_row, s, (j - 1) * P2_BN + g * 64);
+            const int vrow = (int)cache_row_at(p.pages, crow, s, (j - 1) * P2_BN + g * 64);
 #pragma unroll
             for (int a = 0; a < 2; ++a)
               tma_load_2d_pair(ring + sl * P2_SLOT + a * 8192, &mapV, bar, kvh * HEAD_DIM + (int)rank * 128 + a * 64, vrow);
@@ -285,7 +286,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         ok = __all_sync(0xffffffffu, ok);
         if (ok && elect_one()) {
           mbar_expect_tx(&ctl->fix_bar, P2_SLOT);
-          const int vrow = (int)cache_row_of(p.pages, p.cache_row, s, (nt - 1) * P2_BN + g * 64);
+          const int vrow = (int)cache_row_at(p.pages, crow, s, (nt - 1) * P2_BN + g * 64);
 #pragma unroll
           for (int a = 0; a < 2; ++a)
             tma_load_2d(ring + sl * P2_SLOT + a * 8192, &mapV, &ctl->fix_bar, kvh * HEAD_DIM + (int)rank * 128 + a * 64, vrow);

@@ -168,6 +168,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       int nt, t0, t1;
       while (ok && find_live(u, pre, nt, t0, t1)) {
         const UnitInfo ui = unit_info(p, u);
+        const long long base = p.cache_row ? p.cache_row[ui.s] : 0;
         for (int j = t0; j <= t1 && ok; ++j) {
           if (j < t1) {
             QWB_TL(10, j - t0);
@@ -175,21 +176,22 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
               grid_dep_wait();
               dep_waited = true;
             }
+            const int krow = (int)cache_row_at(p.pages, base, ui.s, j * DU_BN);  // a tile never straddles a page
             for (int c = 0; c < 4 && ok; ++c) {
               if (!slot_ready()) break;
-              tma_load_2d(ring + sl * DU_SLOT, &mapK, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
-                          (int)cache_row_of(p.pages, p.cache_row, ui.s, j * DU_BN));
+              tma_load_2d(ring + sl * DU_SLOT, &mapK, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64, krow);
               advance();
             }
           }
           if (j > t0 && ok) {
             QWB_TL(11, j - 1 - t0);
+            const int vrow = (int)cache_row_at(p.pages, base, ui.s, (j - 1) * DU_BN);
             for (int g = 0; g < 4 && ok; ++g) {
               if (!slot_ready()) break;
 #pragma unroll
               for (int c = 0; c < 4; ++c)  // 32 keys x 64 channels each, channel atoms 4 KB apart
                 tma_load_2d(ring + sl * DU_SLOT + c * 4096, &mapV, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
-                            (int)cache_row_of(p.pages, p.cache_row, ui.s, (j - 1) * DU_BN + g * 32));
+                            vrow + g * 32);
               advance();
             }
           }
@@ -314,28 +316,44 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     auto stage_q = [&](const UnitInfo &ui) {
       const int R = ui.ntok * GROUP;
       if (p.q_dep) grid_dep_wait();  // q comes out of the launch before this one
-      for (int idx = st_tid; idx < p.q_rows_pad * 32; idx += DU_SM_THREADS) {
-        const int r = idx >> 5, c16 = idx & 31;           // 8 channels c16*8 .. +7
-        if (p.do_rope && c16 < 8) continue;               // rotary channels are written pair-wise below
-        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (r < R) {
-          const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + r / GROUP) * p.q_heads + (size_t)ui.kvh * GROUP + r % GROUP;
-          load8<uint16_t>(reinterpret_cast<const uint16_t *>(p.q) + grow * HEAD_DIM + c16 * 8, x);
+      // Two passes of the thread group at a time, with every global load of both issued before the first is
+      // used: a 32-row tile (decode, verify) is staged in one memory round trip instead of four.
+      const int n_items = p.q_rows_pad * 32;  // 8-channel chunks, and as many rotary pairs
+      for (int base = 0; base < n_items; base += 2 * DU_SM_THREADS) {
+        uint4 xq[2];
+        uint16_t rx[2], ry[2];
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+          const int idx = base + it * DU_SM_THREADS + st_tid;
+          const int r = idx >> 5, c16 = idx & 31;           // 8 channels c16*8 .. +7
+          xq[it] = make_uint4(0, 0, 0, 0);
+          rx[it] = ry[it] = 0;
+          if (idx < n_items && r < R) {
+            const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + r / GROUP) * p.q_heads + (size_t)ui.kvh * GROUP + r % GROUP;
+            const uint16_t *src = reinterpret_cast<const uint16_t *>(p.q) + grow * HEAD_DIM;
+            if (!(p.do_rope && c16 < 8)) xq[it] = *reinterpret_cast<const uint4 *>(src + c16 * 8);
+            if (p.do_rope) {  // the same index also names rotary pair (i, i + 32) = (c16, c16 + 32) of row r
+              rx[it] = src[c16];
+              ry[it] = src[c16 + ROT_PAIRS];
+            }
+          }
         }
-        *reinterpret_cast<uint4 *>(q_smem + q_tile_off(r, c16 * 8, QSUB)) =
-            make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
-      }
-      if (p.do_rope) {
-        for (int idx = st_tid; idx < p.q_rows_pad * ROT_PAIRS; idx += DU_SM_THREADS) {
-          const int r = idx / ROT_PAIRS, i = idx % ROT_PAIRS;  // pair (i, i + 32) of row r
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+          const int idx = base + it * DU_SM_THREADS + st_tid;
+          if (idx >= n_items) continue;
+          const int r = idx >> 5, c16 = idx & 31;
+          if (!(p.do_rope && c16 < 8))                      // rotary channels are written pair-wise below
+            *reinterpret_cast<uint4 *>(q_smem + q_tile_off(r, c16 * 8, QSUB)) = xq[it];
+          if (!p.do_rope) continue;
+          const int i = c16;
           float xr = 0.f, yr = 0.f;
           if (r < R) {
             const size_t trow = (size_t)ui.s * p.n_new + ui.tok0 + r / GROUP;
-            const uint16_t *src = reinterpret_cast<const uint16_t *>(p.q) + (trow * p.q_heads + (size_t)ui.kvh * GROUP + r % GROUP) * HEAD_DIM;
-            const float x = bf16_bits_to_f32(src[i]), y = bf16_bits_to_f32(src[i + ROT_PAIRS]);
             const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.pos + ui.tok0 + r / GROUP;
             float c, sn;
             rope_sincos_reduced(pz, p.rope.inv_freq[i], c, sn);
+            const float x = bf16_bits_to_f32(rx[it]), y = bf16_bits_to_f32(ry[it]);
             xr = x * c - y * sn;
             yr = x * sn + y * c;
           }
