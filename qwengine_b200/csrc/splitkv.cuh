@@ -330,9 +330,17 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   int pt = (int)(max(g0, ppre) - ppre);              // next tile within the unit
   uint32_t pit = 0;                                  // tiles issued so far
   bool pok = true, dep_waited = false;
+  int cached_u = -1;                                 // unit whose description and base row are held below:
+  UnitInfo cached_ui;                                // loads issued while the SM streams K/V are slow, so the
+  long long cached_base = 0;                         // producer reads them once per unit, not once per tile
   auto produce_one = [&]() -> bool {
     while (ppre < g1 && pu < n_units) {
-      const UnitInfo ui = unit_info(p, pu);
+      if (pu != cached_u) {
+        cached_ui = unit_info(p, pu);
+        cached_base = p.cache_row ? p.cache_row[cached_ui.s] : 0;
+        cached_u = pu;
+      }
+      const UnitInfo &ui = cached_ui;
       const int nt = (ui.len + SK_TK - 1) / SK_TK;
       const int t1 = (int)(min(g1, ppre + nt) - ppre);
       if (pt < t1) {
@@ -349,7 +357,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         }
         uint8_t *kd = stage_base + st * SK_STAGE_BYTES, *vd = kd + SK_TILE_BYTES;
         mbar_expect_tx(&full[st], SK_STAGE_BYTES);
-        const int r = (int)cache_row_of(p.pages, p.cache_row, ui.s, pt * SK_TK);
+        const int r = (int)cache_row_at(p.pages, cached_base, ui.s, pt * SK_TK);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           tma_load_2d(kd + c * (SK_TK * 128), &mapK, &full[st], ui.kvh * HEAD_DIM + c * 64, r);
