@@ -340,3 +340,18 @@ def test_fused_mixer_step_in_a_cuda_graph():
     assert np.array_equal(host_f32(out).reshape(-1, 24, 256), eager)
     assert np.array_equal(lse.cpu().numpy().reshape(-1, 24), lse_eager)
     assert np.array_equal(host_bits(kc), kc_eager)
+
+
+@pytest.mark.parametrize("hist,n_new", [([3000, 700], 1), ([2500], 4), ([600], 300)])
+def test_growing_logits_force_rescales(hist, n_new):
+    """Keys whose scale grows along the sequence (and one late outlier) make the running maximum rise tile after
+    tile, so every kernel's deferred rescale of O and l is exercised, far from the N(0,1) comfort zone."""
+    c = Case(90 + n_new, hist, n_new)
+    for s in range(c.n_seq):
+        r0, h = int(c.cache_row[s]), int(c.hist[s])
+        k = O.bf16_bits_to_f32(c.kc0[r0:r0 + h])
+        ramp = (0.25 + 3.0 * np.arange(h, dtype=np.float32) / max(h, 1))[:, None]
+        k = k * ramp
+        k[h - 7] *= 3.0  # a late outlier key
+        c.kc0[r0:r0 + h] = O.f32_to_bf16_bits(k.astype(np.float32))
+    _full_check(c, "growing logits")
