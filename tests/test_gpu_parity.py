@@ -355,3 +355,13 @@ def test_growing_logits_force_rescales(hist, n_new):
         k[h - 7] *= 3.0  # a late outlier key
         c.kc0[r0:r0 + h] = O.f32_to_bf16_bits(k.astype(np.float32))
     _full_check(c, "growing logits")
+
+
+@pytest.mark.parametrize("n_new", [1, 3])
+def test_many_short_sequences_per_cta(n_new):
+    """Far more units than CTAs: every CTA walks through many whole units (and shares at most its first and its
+    last with a neighbour), which exercises the unit-change path and the ring phases of both split-KV kernels."""
+    rng = np.random.default_rng(95)
+    hist = rng.integers(0, 700, 311).tolist()
+    hist[5], hist[77] = 0, 1
+    _full_check(Case(95 + n_new, hist, n_new), "many short sequences")
