@@ -365,3 +365,10 @@ def test_many_short_sequences_per_cta(n_new):
     hist = rng.integers(0, 700, 311).tolist()
     hist[5], hist[77] = 0, 1
     _full_check(Case(95 + n_new, hist, n_new), "many short sequences")
+
+
+@pytest.mark.parametrize("n_new", [10, 11, 21, 22, 63])
+def test_short_chunks_all_tile_layouts(n_new):
+    """Chunk lengths around the row-tile limits of the tcgen05 split-KV kernel: 10 / 11 tokens (60 / 66 rows: the
+    64- and 128-row Q tiles), 21 (126 rows, one block) and 22, 63 (two and three blocks per sequence and KV head)."""
+    _full_check(Case(120 + n_new, [513, 64, 1290], n_new, kv_heads=2), "chunk of %d" % n_new)
