@@ -590,8 +590,12 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           for (int i = 0; i <= c_last - c_first; ++i)
             nparts += i < DU_MAX_PARTS ? ctl->merge_live[k][i] : ((total * (c_first + i) / G != total * (c_first + i + 1) / G) ? 1 : 0);
           ctl->merge_parts[k] = nparts;
-          ctl->ticket[k] = atomicAdd(&p.cnt[pend_u[k]], 1);
         }
+        // both tickets in flight together (one memory round trip), not one after the other
+        const int tk0 = (go && n_pend > 0) ? atomicAdd(&p.cnt[pend_u[0]], 1) : 0;
+        const int tk1 = (go && n_pend > 1) ? atomicAdd(&p.cnt[pend_u[1]], 1) : 0;
+        ctl->ticket[0] = tk0;
+        ctl->ticket[1] = tk1;
         __threadfence();
         ctl->merge_go = go;
       }
