@@ -283,7 +283,7 @@ int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   CUtensorMap mk, mv;
   int rc = make_rowmajor_map(&mk, c.kc, c.cache_rows, c.kv_heads * HEAD_DIM, 128);
   if (rc) return rc;
-  rc = make_rowmajor_map(&mv, c.vc, c.cache_rows, c.kv_heads * HEAD_DIM, 32);
+  rc = make_rowmajor_map(&mv, c.vc, c.cache_rows, c.kv_heads * HEAD_DIM, 64);
   if (rc) return rc;
 #ifdef QWB_TIMELINE
   p.dbg = qwb::g_timeline_buf; p.dbg_block = qwb::g_timeline_block;

@@ -28,8 +28,8 @@ namespace qwb {
 namespace {
 
 constexpr int DU_BN = 128;                 // keys per tile
-constexpr int DU_SLOT = 16384;
-constexpr int DU_MAX_SLOT = 13;            // ring slots when the Q tile is smallest
+constexpr int DU_SLOT = 32768;             // half a K tile (128 keys x 128 channels) or half a V tile (64 keys x 256)
+constexpr int DU_MAX_SLOT = 6;             // ring slots when the Q tile is smallest
 constexpr int DU_SMEM_TOTAL = 232448 - 1024;   // dynamic shared memory left after the alignment slack
 constexpr int DU_NWG = 4;
 constexpr int DU_MAX_PARTS = 256;         // CTAs of one unit whose liveness is tabulated for the merge
@@ -146,7 +146,8 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   if (warp == 0) {
     // =============================== TMA producer ===========================================
     // Per segment the slot stream is  K_t0 | K_t0+1 V_t0 | ... | V_t1-1 ; segments follow each
-    // other without a gap.  A K slot is one 64-channel sub-tile of 128 keys, a V slot 32 keys x 256.
+    // other without a gap.  A K slot is two 64-channel sub-tiles of 128 keys, a V slot 64 keys x 256 channels
+    // (32 KB each: fewer, larger slots keep the issuing thread's waits and commits off the tensor pipe's path).
     if (elect_one()) {
       int u = (int)ctl->part[2];
       long long pre = ctl->part[1];
@@ -177,21 +178,24 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
               dep_waited = true;
             }
             const int krow = (int)cache_row_at(p.pages, base, ui.s, j * DU_BN);  // a tile never straddles a page
-            for (int c = 0; c < 4 && ok; ++c) {
+            for (int c2 = 0; c2 < 2 && ok; ++c2) {  // two 64-channel sub-tiles per slot
               if (!slot_ready()) break;
-              tma_load_2d(ring + sl * DU_SLOT, &mapK, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64, krow);
+#pragma unroll
+              for (int a = 0; a < 2; ++a)
+                tma_load_2d(ring + sl * DU_SLOT + a * 16384, &mapK, &ctl->slot_full[sl],
+                            ui.kvh * HEAD_DIM + (2 * c2 + a) * 64, krow);
               advance();
             }
           }
           if (j > t0 && ok) {
             QWB_TL(11, j - 1 - t0);
             const int vrow = (int)cache_row_at(p.pages, base, ui.s, (j - 1) * DU_BN);
-            for (int g = 0; g < 4 && ok; ++g) {
+            for (int g = 0; g < 2 && ok; ++g) {
               if (!slot_ready()) break;
 #pragma unroll
-              for (int c = 0; c < 4; ++c)  // 32 keys x 64 channels each, channel atoms 4 KB apart
-                tma_load_2d(ring + sl * DU_SLOT + c * 4096, &mapV, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
-                            vrow + g * 32);
+              for (int c = 0; c < 4; ++c)  // 64 keys x 64 channels each, channel atoms 8 KB apart
+                tma_load_2d(ring + sl * DU_SLOT + c * 8192, &mapV, &ctl->slot_full[sl], ui.kvh * HEAD_DIM + c * 64,
+                            vrow + g * 64);
               advance();
             }
           }
@@ -209,7 +213,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     const uint32_t idesc_pv = make_idesc(128, 256, 1, 1, 0, 1);
     const uint64_t qdesc0 = smem_desc(smem_u32(q_smem), 16, 1024);
     const uint64_t kdesc0 = smem_desc(smem_u32(ring), 16, 1024);
-    const uint64_t vdesc0 = smem_desc(smem_u32(ring), 4096, 1024);
+    const uint64_t vdesc0 = smem_desc(smem_u32(ring), 8192, 1024);  // channel atoms 8 KB apart, 8-key groups 1 KB
     const uint32_t qsub16 = (uint32_t)(QSUB >> 4);
     int u = (int)ctl->part[2];
     long long pre = ctl->part[1];
@@ -238,11 +242,13 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           // ---- S[Jt & 1] = Q K_j^T ----
           const uint32_t d_s = tmem + ((Jt & 1) ? TMEM_S1 : TMEM_S0);
           QWB_TL(0, Jt); QWB_TL(31, Jt);
-          for (int c = 0; c < 4 && ok; ++c) {
+          for (int c2 = 0; c2 < 2 && ok; ++c2) {  // a slot = two 64-channel sub-tiles of the K tile
             if (!wait_all(&ctl->slot_full[sl], ph, DEV_ERR_MMA_WAIT)) break;
             tc_fence_after();
-            {
-              const uint64_t kd = kdesc0 + (uint64_t)(sl * (DU_SLOT >> 4));
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+              const int c = 2 * c2 + a;
+              const uint64_t kd = kdesc0 + (uint64_t)((sl * DU_SLOT + a * 16384) >> 4);
               const uint64_t qd = qdesc0 + (uint64_t)(c * qsub16);
 #pragma unroll
               for (int k = 0; k < 4; ++k) umma_ss(d_s, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_qk, (c | k) != 0);
@@ -251,9 +257,9 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_ss(d_s, ql + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_qk, 1);
               }
-              umma_commit(&ctl->slot_empty[sl]);
-              if (c == 3) umma_commit(&ctl->s_full[Jt & 1]);
             }
+            umma_commit(&ctl->slot_empty[sl]);
+            if (c2 == 1) umma_commit(&ctl->s_full[Jt & 1]);
             advance();
           }
         }
@@ -267,20 +273,18 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           tc_fence_after();
           QWB_TL(2, Jp);
           const uint32_t a_p = tmem + ((Jp & 1) ? TMEM_S1 : TMEM_S0);
-          for (int g = 0; g < 4 && ok; ++g) {
+          for (int g = 0; g < 2 && ok; ++g) {  // a slot = 64 keys of the V tile
             if (!wait_all(&ctl->slot_full[sl], ph, DEV_ERR_MMA_WAIT)) break;
             tc_fence_after();
-            {
-              const uint64_t vd = vdesc0 + (uint64_t)(sl * (DU_SLOT >> 4));
-              const uint32_t first = (uint32_t)(jj != t0) | (uint32_t)g;
+            const uint64_t vd = vdesc0 + (uint64_t)(sl * (DU_SLOT >> 4));
+            const uint32_t first = (uint32_t)(jj != t0) | (uint32_t)g;
 #pragma unroll
-              for (int k = 0; k < 2; ++k) {
-                umma_ts(tmem + TMEM_O, a_p + (g * 2 + k) * 8, vd + (uint64_t)(k * 128), idesc_pv, first | (uint32_t)k);
-                umma_ts(tmem + TMEM_O, a_p + 64 + (g * 2 + k) * 8, vd + (uint64_t)(k * 128), idesc_pv, 1);
-              }
-              umma_commit(&ctl->slot_empty[sl]);
-              if (g == 3) umma_commit(&ctl->o_done[Jp & 1]);
+            for (int k = 0; k < 4; ++k) {  // 16 keys per step: 2 KB further in every channel atom
+              umma_ts(tmem + TMEM_O, a_p + (g * 4 + k) * 8, vd + (uint64_t)(k * 128), idesc_pv, first | (uint32_t)k);
+              umma_ts(tmem + TMEM_O, a_p + 64 + (g * 4 + k) * 8, vd + (uint64_t)(k * 128), idesc_pv, 1);
             }
+            umma_commit(&ctl->slot_empty[sl]);
+            if (g == 1) umma_commit(&ctl->o_done[Jp & 1]);
             advance();
           }
           QWB_TL(3, Jp);
@@ -465,20 +469,20 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         }
         // Keys past the end of the unit may hold anything in V; P is zero there but 0 * NaN is NaN,
         // so those rows are cleared before the tensor core reads them.  The ragged tile is the
-        // unit's last, hence the last of its segment: its V slots are the four that follow the
-        // 8 Jt + 4 slots consumed before them.
+        // unit's last, hence the last of its segment: its V slots are the two that follow the
+        // 4 Jt + 2 slots consumed before them.
         if (j * DU_BN + DU_BN > ui.len) {
-          for (int g = 0; g < 4; ++g) {
-            const int key_lo = j * DU_BN + g * 32;
-            if (key_lo + 32 <= ui.len) continue;
-            const uint32_t itv = 8u * (uint32_t)Jt + 4u + (uint32_t)g;
+          for (int g = 0; g < 2; ++g) {
+            const int key_lo = j * DU_BN + g * 64;
+            if (key_lo + 64 <= ui.len) continue;
+            const uint32_t itv = 4u * (uint32_t)Jt + 2u + (uint32_t)g;
             const int sl = (int)(itv % (uint32_t)DU_NSLOT);
             if (ok) ok = wait_or_abort(&ctl->slot_full[sl], (itv / (uint32_t)DU_NSLOT) & 1u, abort_flag);
             const int valid = max(0, ui.len - key_lo);
-            for (int idx = st_tid; idx < 32 * 32; idx += DU_SM_THREADS) {
+            for (int idx = st_tid; idx < 64 * 32; idx += DU_SM_THREADS) {
               const int kr = idx >> 5, c16 = idx & 31;
               if (kr >= valid)
-                *reinterpret_cast<uint4 *>(ring + sl * DU_SLOT + (c16 >> 3) * 4096 + kr * 128 + (((c16 & 7) ^ (kr & 7)) << 4)) =
+                *reinterpret_cast<uint4 *>(ring + sl * DU_SLOT + (c16 >> 3) * 8192 + kr * 128 + (((c16 & 7) ^ (kr & 7)) << 4)) =
                     make_uint4(0, 0, 0, 0);
             }
           }
