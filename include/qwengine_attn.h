@@ -77,9 +77,15 @@ int qw_kv_append_f32(const float *k, const float *v, qw_bf16 *kc, qw_bf16 *vc,
 
 /* Decode / speculative-verify attention: row b of q[B][q_heads][dim] attends to the
  * first *dpos + b + 1 cache rows (its own included).  `scratch` is the reference's
- * score workspace (B * q_heads * ctx floats); here it holds split-KV partials and
- * must be at least qw_attn_decode_scratch_floats() floats, which never exceeds the
- * reference's size for ctx >= 512.  ctx is the number of rows in kc / vc.  1 <= B <= 8.
+ * score workspace and MUST hold B * q_heads * ctx floats, 16-byte aligned -- what the
+ * reference's own kernel needs at the same launch (src/mixers.cu:441, rt.scores at
+ * src/model.cu:168, M.scores at src/mtp.cu:115).  The launcher uses exactly that many floats
+ * (qw_attn_decode_scratch_floats() returns the same number) for split-KV partials and
+ * arrival counters: the more there are, the more CTAs share a sequence; if they do not
+ * even hold one CTA's partial (ctx below about 128) the call returns QW_ERR_WORKSPACE.
+ * ctx is the number of rows in kc / vc.  1 <= B <= 8.  The bf16 flavour runs B >= 2 on the
+ * tcgen05 split-KV kernel; the fp32 flavour keeps q exact (bf16 hi + lo on all channels)
+ * on the mma.sync kernel.
  * Replaces k_attn_decode<<<dim3(q_heads, B), 256>>>: src/mixers.cu:436-525;
  * launched at src/model.cu:236-238, src/mtp.cu:176-178. */
 int qw_attn_decode_bf16(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out,
@@ -110,8 +116,12 @@ int qw_attn_decode_bf16_noalloc(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf
                                 int ctx, int B, qw_stream stream);
 
 /* Chunked-prefill attention: row t of q[T][q_heads][dim] attends to the first
- * *dpos + t + 1 cache rows.  `scratch` (reference: T * q_heads * ctx floats) is used
- * only by the fallback kernel; qw_attn_prefill_scratch_floats() gives the minimum.
+ * *dpos + t + 1 cache rows.  Chunks of T >= 64 rows run on the tcgen05 CTA-pair kernel,
+ * shorter ones on the split-KV kernels.  `scratch` (reference: T * q_heads * ctx floats,
+ * src/prefill.cu:75) must hold qw_attn_prefill_scratch_floats() floats, 16-byte aligned:
+ * split-KV partials for short chunks and, in the fp32 flavour with T >= 64, the bf16 copy
+ * of q that the tensor cores read (q is rounded to bf16 there, exactly as k is when it
+ * enters the bf16 cache; short chunks keep q exact).
  * Replaces k_attn_prefill<<<dim3(q_heads, ceil(T/8)), 256>>>: src/mixers.cu:546-649;
  * launched at src/prefill.cu:152-154. */
 int qw_attn_prefill_bf16(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out,
@@ -145,11 +155,9 @@ enum {
   QW_F_NO_UMMA = 16,   /* force the split-KV kernel even for long prefill chunks        */
   QW_F_FAST_P = 32,    /* tcgen05 prefill only: feed P as one bf16 instead of a bf16 hi+lo
                           pair; 1/3 less tensor work, output rel-L2 ~1.4e-3 instead of 2e-6 */
-  QW_F_UMMA_1CTA = 64, /* tcgen05 prefill only: use the single-CTA kernel instead of the CTA-pair
-                          (cta_group::2) kernel                                            */
   QW_F_NO_CAUSAL = 128 /* every row sees exactly pos[s] (>= 1) keys of its sequence: the call covers
                           a KV sub-range that does not contain the new rows (cross-GPU KV split);
-                          excludes QW_F_APPEND, q must arrive rotated                       */
+                          excludes QW_F_APPEND; with QW_F_ROPE the descriptor must carry q_pos    */
 };
 
 typedef struct qw_mixer_desc {
@@ -189,6 +197,13 @@ typedef struct qw_mixer_desc {
   const int *block_table;
   int block_table_stride;
   int page_rows;
+  /* Optional, device, [n_seq]: absolute position of each sequence's first new row, used for the RoPE
+   * angles (row b rotates by q_pos[s] + b) instead of pos[s].  A call that covers a KV sub-range of a
+   * sequence (cross-GPU KV split) counts keys from the start of its range in pos[s] while its rows sit at
+   * their absolute positions; with q_pos such a call rotates q (and, with QW_F_APPEND, k) itself, in
+   * fp32 like every other call.  NULL (a zeroed descriptor): angles come from pos[s].  mpos, when given,
+   * wins over both.  No counterpart in the reference (one GPU, one range). */
+  const int *q_pos;
 } qw_mixer_desc;
 
 size_t qw_mixer_workspace_bytes(const qw_mixer_desc *d);
@@ -196,6 +211,10 @@ int qw_mixer_forward(const qw_mixer_desc *d, qw_stream stream);
 
 /* Number of kernels the last qw_* call on this thread launched (for launch accounting). */
 int qw_last_launch_count(void);
+/* Name of the attention kernel that the last attention call on this thread launched: "splitkv_kernel"
+ * (mma.sync), "splitkv_umma_kernel" or "prefill_umma_pair_kernel" (tcgen05); "" if it launched none.
+ * For tests and benchmarks that must know which kernel a route reaches.  No counterpart in the reference. */
+const char *qw_last_attention_kernel(void);
 
 /* Instrumentation for benchmarks.  While enabled (per host thread), every attention call
  * records a CUDA event pair around its dominant kernel (split-KV or tcgen05 prefill) on the
@@ -222,7 +241,8 @@ int qw_mixer_forward_fused(const qw_mixer_desc *d, const void *fused, int fused_
  *
  * A partial is, per (row, q_head), QW_PARTIAL_FLOATS floats: o[256] un-normalised fp32,
  * m (running max of scale*log2(e)*score) and l (sum of exp2), then two pad floats.
- * qw_mixer_forward_partial() runs the mixer but emits partials [n_seq*n_new][q_heads][260]
+ * qw_mixer_forward_partial() runs the mixer (any kernel but the tcgen05 prefill one: chunks of 64
+ * rows or more use the split-KV kernels here) but emits partials [n_seq*n_new][q_heads][260]
  * instead of normalised output; after the ranks exchange them (NCCL, outside this library)
  * qw_combine_partials() merges n_parts of them, laid out [n_parts][rows][q_heads][260], in
  * index order (fixed order => bit-stable) and applies the gate (QW_F_GATE, QW_F_OUT_F32).
@@ -238,8 +258,10 @@ int qw_combine_partials(const float *parts, int n_parts, int64_t rows, int q_hea
  * mapping of rank k's partial buffer [rows][q_heads][260] and of rank k's flag word (symmetric memory, CUDA IPC
  * or any other peer mapping; the flag words start at zero).  Every rank calls it with the same `step`
  * (1, 2, 3, ...) after the launch that wrote its own partials on the same stream; the kernel publishes the step
- * in the rank's own flag, waits (at most two seconds, else *status = 106 and the output is left alone) until
- * every peer has published it, then reads the peers' partials in place.  Alternate two buffer / flag sets by
+ * in the rank's own flag, waits (at most two seconds, else *status = 106) until
+ * every peer has published it, then reads the peers' partials in place.  The wait is per thread block: if
+ * *status is 106 afterwards, blocks that saw the peers in time have written their rows and the others have
+ * not, so the whole output must be treated as undefined.  Alternate two buffer / flag sets by
  * step parity.  No counterpart in the reference (single GPU). */
 int qw_combine_partials_peer(const float *const *part_ptrs, int *const *flag_ptrs, int rank, int n_parts, int step,
                              int64_t rows, int q_heads, const qw_bf16 *gate, void *out, float *lse, int flags,

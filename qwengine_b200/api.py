@@ -8,6 +8,7 @@ there is no fallback: a missing or unloadable library raises.
 """
 import ctypes as C
 import os
+import shutil
 
 import torch
 
@@ -17,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libqwengine_attn.so")
 
 QW_OK = 0
-F_ROPE, F_APPEND, F_GATE, F_OUT_F32, F_NO_UMMA, F_FAST_P, F_UMMA_1CTA, F_NO_CAUSAL = 1, 2, 4, 8, 16, 32, 64, 128
+F_ROPE, F_APPEND, F_GATE, F_OUT_F32, F_NO_UMMA, F_FAST_P, F_NO_CAUSAL = 1, 2, 4, 8, 16, 32, 128
 PARTIAL_FLOATS = 260
 HEAD_DIM, ROTARY_DIM, GROUP = 256, 64, 6
 
@@ -31,7 +32,7 @@ class MixerDesc(C.Structure):
         ("q", _vp), ("k_new", _vp), ("v_new", _vp), ("gate", _vp), ("out", _vp), ("lse", _vp),
         ("kc", _vp), ("vc", _vp), ("cache_rows", C.c_int64), ("cache_row", _vp), ("pos", _vp),
         ("mpos", _vp), ("workspace", _vp), ("workspace_bytes", C.c_size_t), ("status", _vp),
-        ("block_table", _vp), ("block_table_stride", _i), ("page_rows", _i),
+        ("block_table", _vp), ("block_table_stride", _i), ("page_rows", _i), ("q_pos", _vp),
     ]
 
 
@@ -41,6 +42,7 @@ _SIGS = {
     "qw_abi_version": (_i, []),
     "qw_last_cuda_error": (C.c_char_p, []),
     "qw_last_launch_count": (_i, []),
+    "qw_last_attention_kernel": (C.c_char_p, []),
     "qw_profile_enable": (_i, [_i]),
     "qw_profile_last_kernel_ms": (_i, [C.POINTER(C.c_float)]),
     "qw_rope_bf16": (_i, [_vp, _i, _i, _i, _vp, _f, _vp, _i, _vp]),
@@ -72,7 +74,9 @@ def lib():
     it can be neither found nor built -- there is deliberately no other implementation."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        # build() is a no-op when the library is newer than every source; without a compiler (a box that
+        # only received the prebuilt file) the existing library is used as it is
+        if shutil.which(os.environ.get("NVCC", "nvcc")) or not os.path.exists(LIB_PATH):
             _build.build()
         l = C.CDLL(LIB_PATH)
         for name, (res, args) in _SIGS.items():
@@ -165,7 +169,7 @@ class Mixer:
         self._keep = None
 
     def bind(self, q, kc, vc, pos, out, k_new=None, v_new=None, gate=None, lse=None, cache_row=None,
-             mpos=None, flags=F_ROPE | F_APPEND | F_GATE, fused=False, block_table=None, page_rows=0):
+             mpos=None, flags=F_ROPE | F_APPEND | F_GATE, fused=False, block_table=None, page_rows=0, q_pos=None):
         d = self.desc
         if out.dtype == torch.float32:
             flags |= F_OUT_F32
@@ -182,7 +186,9 @@ class Mixer:
         d.block_table = _addr(block_table)
         d.block_table_stride = 0 if block_table is None else int(block_table.shape[-1])
         d.page_rows = int(page_rows)
-        self._keep = (q, kc, vc, pos, out, k_new, v_new, gate, lse, cache_row, mpos, block_table)
+        # absolute position of each sequence's first new row, when pos counts keys of a KV sub-range only
+        d.q_pos = _addr(q_pos)
+        self._keep = (q, kc, vc, pos, out, k_new, v_new, gate, lse, cache_row, mpos, block_table, q_pos)
         return self
 
     def forward(self, stream=None):
@@ -207,6 +213,11 @@ class Mixer:
         code = int(self.status.item())
         if code:
             raise QwError("kernel reported device error code %d" % code)
+
+
+def last_attention_kernel():
+    """Name of the attention kernel that the last attention call on this thread launched."""
+    return lib().qw_last_attention_kernel().decode()
 
 
 def profile_enable(on=True):

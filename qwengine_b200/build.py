@@ -10,14 +10,14 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libqwengine_attn.so")
-SOURCES = ["capi.cu", "prefill_umma.cu", "prefill_umma2.cu", "splitkv_umma.cu"]
+SOURCES = ["capi.cu", "prefill_umma2.cu", "splitkv_umma.cu"]
 
 
 def nvcc_cmd(verbose=False):
     cmd = [
         os.environ.get("NVCC", "nvcc"), "-O3", "-std=c++17",
         "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-        "-Xcompiler", "-fPIC", "-shared", "--use_fast_math=false" if False else "-DQWB_BUILD",
+        "-Xcompiler", "-fPIC", "-shared",
         "-o", LIB,
     ]
     if verbose:

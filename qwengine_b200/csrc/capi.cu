@@ -2,6 +2,7 @@
 // construction and kernel launches.  Nothing here allocates, frees or synchronises.
 #include "../../include/qwengine_attn.h"
 
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -16,17 +17,12 @@
 
 using namespace qwb;
 
-#ifdef QWB_TIMELINE
-namespace qwb {
-unsigned long long *g_timeline_buf = nullptr;
-int g_timeline_block = 0;
-}  // namespace qwb
-#endif
 
 namespace {
 
 thread_local char g_cuda_err[256] = "";
 thread_local int g_launches = 0;
+thread_local const char *g_attn_kernel = "";  // attention kernel of the last call on this thread
 
 int cuda_fail(cudaError_t e, const char *what) {
   snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
@@ -44,15 +40,49 @@ int check_launch(const char *what) {
   return e == cudaSuccess ? QW_OK : cuda_fail(e, what);
 }
 
-// Optional event pair around the dominant kernel of a call (see qw_profile_enable).
+constexpr int MAX_DEVICES = 64;
+// Current device, or -1 when it cannot be told or lies outside the per-device tables below.
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -1;
+  return dev;
+}
+
+// Optional event pair around the dominant kernel of a call (see qw_profile_enable).  Events belong
+// to a device, so each host thread keeps one pair per device it has profiled on; g_prof_dev is the
+// device of the last complete pair.
 thread_local bool g_prof_on = false;
-thread_local cudaEvent_t g_prof_ev[2] = {nullptr, nullptr};
-thread_local bool g_prof_valid = false;
+thread_local cudaEvent_t g_prof_ev[MAX_DEVICES][2] = {};
+thread_local int g_prof_dev = -1;
+thread_local bool g_prof_open = false;
 void prof_mark(int which, cudaStream_t st) {
-  if (g_prof_on && g_prof_ev[which]) {
-    cudaEventRecord(g_prof_ev[which], st);
-    if (which == 1) g_prof_valid = true;
+  if (!g_prof_on) return;
+  const int dev = current_device();
+  if (dev < 0) return;
+  if (!g_prof_ev[dev][0] &&
+      (cudaEventCreate(&g_prof_ev[dev][0]) != cudaSuccess || cudaEventCreate(&g_prof_ev[dev][1]) != cudaSuccess)) {
+    cudaGetLastError();
+    return;
   }
+  if (which == 0) {
+    g_prof_dev = -1;
+    g_prof_open = cudaEventRecord(g_prof_ev[dev][0], st) == cudaSuccess;
+  } else if (g_prof_open && cudaEventRecord(g_prof_ev[dev][1], st) == cudaSuccess) {
+    g_prof_dev = dev;
+  }
+  if (which == 1) g_prof_open = false;
+}
+
+// One-time, per-device set-up steps (kernel attributes) may be reached from several host threads at
+// once.  The steps are idempotent, so an atomic flag per device is enough: two threads may both run a
+// step, none reads a half-written flag.
+template <typename F>
+int once_per_device(std::atomic<int> (&done)[MAX_DEVICES], F &&step) {
+  const int dev = current_device();
+  if (dev >= 0 && done[dev].load(std::memory_order_acquire)) return QW_OK;
+  const int rc = step();
+  if (rc == QW_OK && dev >= 0) done[dev].store(1, std::memory_order_release);
+  return rc;
 }
 
 bool geometry_ok(int dim, int kv_heads, int q_heads) {
@@ -66,15 +96,15 @@ RopeTable make_rope_table(float theta, int rot) {
 }
 
 int sm_count() {
-  static int cached[64] = {0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (!cached[dev]) {
-    int n = 0;
+  static std::atomic<int> cached[MAX_DEVICES];
+  const int dev = current_device();
+  if (dev < 0) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (!n) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 // cuTensorMapEncodeTiled through the runtime's entry-point lookup: no link-time libcuda.
@@ -131,11 +161,13 @@ struct AttnCall {
   const int64_t *cache_row;
   PageMap pages;
   const int *pos;
+  const int *q_pos;
   const int *mpos;
   int n_seq, n_new, q_heads, kv_heads;
   float theta, scale;
   bool do_rope, do_gate, no_causal;
   bool q_dep;  // q / gate are produced by the launch before the attention kernel (fused projection rows)
+  bool pdl;    // the launch right before the attention kernel is this call's append kernel: overlap with it
   float *ws;
   size_t ws_floats;
   int *cnt;  // zeroed arrival counters (one per unit) or null
@@ -146,25 +178,30 @@ int splitkv_rb(int n_new) { return n_new < 5 ? n_new : 5; }  // tokens per unit:
 size_t splitkv_slot_floats(int rb) { return (size_t)rb * GROUP * PART_STRIDE; }
 
 template <int MT, int DS, int STAGES, int LOK, typename TIn, typename TOut>
-int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, cudaStream_t st) {
+int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, cudaStream_t st, bool pdl) {
   // The 8-warp block (producer folded into warp 0) leaves every thread up to 255 registers, which the
   // two-row-tile variant needs.  The one-tile variant is faster with its dedicated producer warp:
   // folded, with Q fragments in registers, config 2 took 140 us instead of 104 us.
   constexpr bool FOLD = MT > 1;
   auto kern = splitkv_kernel<MT, DS, STAGES, LOK, FOLD, TIn, TOut>;
   constexpr size_t smem = splitkv_smem_bytes<MT, DS, STAGES>();
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
+  static std::atomic<int> configured[MAX_DEVICES];
+  int rc = once_per_device(configured, [&]() -> int {
     QW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[dev] = true;
-  }
+    return QW_OK;
+  });
+  if (rc) return rc;
+  g_attn_kernel = "splitkv_kernel";
   prof_mark(0, st);
-  // with arrival counters the launch follows this step's append kernel: start while that one still runs
-  launch_kernel(kern, dim3(p.G), dim3((SK_KS * DS + (FOLD ? 0 : 1)) * 32), smem, st, p.cnt != nullptr, mk, mv, p);
+  // behind this step's append kernel the launch is a programmatic dependent: it starts while that one still runs
+  const cudaError_t le =
+      launch_kernel(kern, dim3(p.G), dim3((SK_KS * DS + (FOLD ? 0 : 1)) * 32), smem, st, pdl, mk, mv, p);
   prof_mark(1, st);
-  int rc = check_launch("splitkv_kernel");
+  if (le != cudaSuccess) {
+    ++g_launches;
+    return cuda_fail(le, "splitkv_kernel");
+  }
+  rc = check_launch("splitkv_kernel");
   if (rc) return rc;
   if (p.cnt) return QW_OK;  // units cut across CTAs were merged by their last CTA
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
@@ -177,20 +214,20 @@ int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKV
 template <int MT, int STAGES>
 int launch_splitkv_mt(const AttnCall &c, const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p,
                       cudaStream_t st) {
-  if (c.q_is_f32) return launch_splitkv_t<MT, 2, STAGES, 16, float, float>(mk, mv, p, st);
+  if (c.q_is_f32) return launch_splitkv_t<MT, 2, STAGES, 16, float, float>(mk, mv, p, st, c.pdl);
   if (c.out_is_f32)
-    return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, float>(mk, mv, p, st)
-                     : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, float>(mk, mv, p, st);
-  return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, uint16_t>(mk, mv, p, st)
-                   : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, uint16_t>(mk, mv, p, st);
+    return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, float>(mk, mv, p, st, c.pdl)
+                     : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, float>(mk, mv, p, st, c.pdl);
+  return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, uint16_t>(mk, mv, p, st, c.pdl)
+                   : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, uint16_t>(mk, mv, p, st, c.pdl);
 }
 
 int launch_splitkv(const AttnCall &c, cudaStream_t st) {
   SplitKVParams p;
   memset(&p, 0, sizeof(p));
   p.q = c.q; p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.partial_out = c.partial_out;
-  p.pos = c.pos; p.cache_row = c.cache_row; p.pages = c.pages; p.mpos = c.mpos; p.ws = c.ws; p.status = c.status;
-  p.cnt = c.partial_out ? nullptr : c.cnt;
+  p.pos = c.pos; p.q_pos = c.q_pos; p.cache_row = c.cache_row; p.pages = c.pages; p.mpos = c.mpos; p.ws = c.ws;
+  p.status = c.status; p.cnt = c.cnt;
   p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.rb = splitkv_rb(c.n_new);
   p.nblk = (c.n_new + p.rb - 1) / p.rb;
@@ -205,9 +242,6 @@ int launch_splitkv(const AttnCall &c, cudaStream_t st) {
   p.q_lo_dims = c.q_is_f32 ? HEAD_DIM : (c.do_rope ? ROTARY_DIM : 0);
   p.scale_log2 = c.scale * LOG2E;
   p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate; p.no_causal = c.no_causal; p.q_dep = c.q_dep;
-#ifdef QWB_TIMELINE
-  p.dbg = qwb::g_timeline_buf; p.dbg_block = qwb::g_timeline_block;
-#endif
   p.rope = make_rope_table(c.theta, ROTARY_DIM);
 
   CUtensorMap mk, mv;
@@ -250,10 +284,12 @@ size_t mixer_slot_floats(int n_seq, int n_new, int kv_heads) {
 // Which split-KV kernel serves chunks of n_new < 64 tokens in the fused path: the tcgen05 one for
 // two or more new tokens (environment QWB_DECODE_KERNEL=umma / mma overrides, for experiments).
 bool prefer_umma_decode(int n_new) {
-  static int mode = -1;
+  static std::atomic<int> cached{-1};
+  int mode = cached.load(std::memory_order_relaxed);
   if (mode < 0) {
     const char *e = getenv("QWB_DECODE_KERNEL");
     mode = !e ? 0 : (e[0] == 'u' ? 1 : (e[0] == 'm' ? 2 : 0));
+    cached.store(mode, std::memory_order_relaxed);
   }
   if (mode == 1) return true;
   if (mode == 2) return false;
@@ -263,8 +299,9 @@ bool prefer_umma_decode(int n_new) {
 int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   SplitKVParams p;
   memset(&p, 0, sizeof(p));
-  p.q = c.q; p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.partial_out = nullptr;
-  p.pos = c.pos; p.cache_row = c.cache_row; p.pages = c.pages; p.mpos = c.mpos; p.ws = c.ws; p.status = c.status; p.cnt = c.cnt;
+  p.q = c.q; p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.partial_out = c.partial_out;
+  p.pos = c.pos; p.q_pos = c.q_pos; p.cache_row = c.cache_row; p.pages = c.pages; p.mpos = c.mpos; p.ws = c.ws;
+  p.status = c.status; p.cnt = c.cnt;
   p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.rb = splitkv_umma_rb(c.n_new);
   p.nblk = (c.n_new + p.rb - 1) / p.rb;
@@ -285,11 +322,9 @@ int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   if (rc) return rc;
   rc = make_rowmajor_map(&mv, c.vc, c.cache_rows, c.kv_heads * HEAD_DIM, 64);
   if (rc) return rc;
-#ifdef QWB_TIMELINE
-  p.dbg = qwb::g_timeline_buf; p.dbg_block = qwb::g_timeline_block;
-#endif
+  g_attn_kernel = "splitkv_umma_kernel";
   prof_mark(0, st);
-  rc = launch_splitkv_umma(mk, mv, p, c.out_is_f32, st, p.cnt != nullptr);
+  rc = launch_splitkv_umma(mk, mv, p, c.out_is_f32, st, c.pdl);
   prof_mark(1, st);
   ++g_launches;
   if (rc == QW_ERR_CUDA) return cuda_fail(cudaGetLastError(), "splitkv_umma_kernel");
@@ -320,63 +355,97 @@ bool desc_ok(const qw_mixer_desc *d, const FusedRows *fr) {
 // memory.  Asking for the same carve-out here spares the SMs a reconfiguration of the L1 / shared
 // split between the two launches of a step.
 void prefer_max_shared_once() {
-  static bool done[64] = {false};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
-  done[dev] = true;
-  cudaFuncSetAttribute(rope_append_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  cudaFuncSetAttribute(fused_rows_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  cudaFuncSetAttribute(fused_rows_kernel<uint16_t>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                       cudaSharedmemCarveoutMaxShared);
-  cudaGetLastError();  // a refusal of the hint is harmless
+  static std::atomic<int> done[MAX_DEVICES];
+  once_per_device(done, []() -> int {
+    cudaFuncSetAttribute(rope_append_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(fused_rows_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(fused_rows_kernel<uint16_t>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaGetLastError();  // a refusal of the hint is harmless
+    return QW_OK;
+  });
+}
+
+// What the split-KV launch of a fused call will be: which kernel, how many units, floats per slot.
+struct SplitPlan {
+  bool umma;
+  long long units;
+  size_t slot;
+};
+SplitPlan split_plan(int n_seq, int n_new, int kv_heads, bool allow_umma) {
+  SplitPlan sp;
+  sp.umma = allow_umma && splitkv_umma_usable(n_new) && prefer_umma_decode(n_new);
+  sp.units = sp.umma ? umma_units(n_seq, n_new, kv_heads) : splitkv_units(n_seq, n_new, kv_heads);
+  sp.slot = splitkv_slot_floats(sp.umma ? splitkv_umma_rb(n_new) : splitkv_rb(n_new));
+  return sp;
 }
 
 int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, const FusedRows *fr = nullptr) {
   g_launches = 0;
+  g_attn_kernel = "";
   if (!desc_ok(d, fr)) return QW_ERR_ARG;
   if (!geometry_ok(d->head_dim, d->kv_heads, d->q_heads) || d->rotary_dim != ROTARY_DIM) return QW_ERR_SHAPE;
   if (d->n_seq == 0 || d->n_new == 0) return QW_OK;
   if ((long long)d->n_seq * d->n_new > (1ll << 30)) return QW_ERR_SHAPE;
   const RopeTable tab = make_rope_table(d->theta, ROTARY_DIM);
-  prefer_max_shared_once();
   PageMap pm = {nullptr, 0, 0};
   if (d->block_table) {
     if (d->page_rows <= 0 || d->page_rows % 128 || d->block_table_stride <= 0) return QW_ERR_ARG;
     pm.table = d->block_table; pm.stride = d->block_table_stride; pm.page_rows = d->page_rows;
   }
   if ((d->flags & QW_F_NO_CAUSAL) && (d->flags & QW_F_APPEND)) return QW_ERR_ARG;  // a sub-range call never owns the new rows
+  // the rows of a sub-range call do not sit at pos[s] + b: their angles need q_pos (or mpos)
+  if ((d->flags & QW_F_NO_CAUSAL) && (d->flags & QW_F_ROPE) && !d->q_pos && !d->mpos) return QW_ERR_ARG;
   const bool use_umma =
       !(d->flags & (QW_F_NO_UMMA | QW_F_NO_CAUSAL)) && !partial && prefill_umma_supported(d->n_new);
-  // Workspace: arrival counters (one per unit), then the split-KV partial slots.  The counters let
-  // the CTA that completes a unit last merge it inside the attention kernel; they must be zero at
-  // launch, which the rope/append kernel of the same call takes care of.
+  // Workspace of the split-KV kernels: arrival counters (one per unit), then the partial slots.  The
+  // counters let the CTA that completes a unit last merge it inside the attention kernel; they must be
+  // zero at launch: the append kernel of the same call clears them, a memset node when there is none.
+  // Everything about the workspace is checked before the first launch, so that an error return means
+  // that nothing was enqueued and nothing (cache, q, gate) was touched.
   const size_t cnt_bytes = mixer_cnt_bytes(d->n_seq, d->n_new, d->kv_heads);
+  const SplitPlan sp = split_plan(d->n_seq, d->n_new, d->kv_heads, !(d->flags & QW_F_NO_UMMA));
   int *cnt = nullptr;
-  if (!use_umma && !partial && (d->flags & QW_F_APPEND) && d->workspace && d->workspace_bytes > cnt_bytes)
+  float *ws = nullptr;
+  size_t ws_floats = 0;
+  if (!use_umma) {
+    if (!d->workspace || (reinterpret_cast<uintptr_t>(d->workspace) & 15) || d->workspace_bytes <= cnt_bytes)
+      return QW_ERR_WORKSPACE;
     cnt = reinterpret_cast<int *>(d->workspace);
-  const long long n_units = (long long)(cnt_bytes / sizeof(int));
+    ws = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(d->workspace) + cnt_bytes);
+    ws_floats = (d->workspace_bytes - cnt_bytes) / sizeof(float);
+    if (sp.units > (1 << 24)) return QW_ERR_SHAPE;
+    if ((long long)(ws_floats / sp.slot) - sp.units < 1) return QW_ERR_WORKSPACE;  // not even one CTA's slot
+  }
+  const int n_zero = cnt ? (int)(cnt_bytes / sizeof(int)) : 0;
+  bool appended = false;
   if (fr) {
+    prefer_max_shared_once();
     const unsigned rows = (unsigned)((size_t)d->n_seq * d->n_new);
     uint16_t *qo = const_cast<uint16_t *>(d->q), *go = const_cast<uint16_t *>(d->gate);
     const int do_rope = (d->flags & QW_F_ROPE) ? 1 : 0;
     if (fr->is_f32)
-      fused_rows_kernel<float><<<dim3(rows, (unsigned)d->kv_heads), 256, 0, st>>>(static_cast<const float *>(fr->rows), fr->q_norm_w, fr->k_norm_w,
-                                                      fr->eps, qo, go, d->kc, d->vc, d->pos, d->cache_row, d->mpos,
-                                                      d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt,
-                                                      cnt ? (int)n_units : 0, pm);
+      fused_rows_kernel<float><<<dim3(rows, (unsigned)d->kv_heads), 256, 0, st>>>(
+          static_cast<const float *>(fr->rows), fr->q_norm_w, fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
+          d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt, n_zero, pm, d->q_pos);
     else
-      fused_rows_kernel<uint16_t><<<dim3(rows, (unsigned)d->kv_heads), 256, 0, st>>>(static_cast<const uint16_t *>(fr->rows), fr->q_norm_w,
-                                                         fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
-                                                         d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads,
-                                                         do_rope, tab, cnt, cnt ? (int)n_units : 0, pm);
+      fused_rows_kernel<uint16_t><<<dim3(rows, (unsigned)d->kv_heads), 256, 0, st>>>(
+          static_cast<const uint16_t *>(fr->rows), fr->q_norm_w, fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
+          d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt, n_zero, pm, d->q_pos);
     int rc = check_launch("fused_rows_kernel");
     if (rc) return rc;
+    appended = true;
   } else if (d->flags & QW_F_APPEND) {
+    prefer_max_shared_once();
     rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
         d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
-        (d->flags & QW_F_ROPE) ? 1 : 0, tab, cnt, cnt ? (int)n_units : 0, pm);
+        (d->flags & QW_F_ROPE) ? 1 : 0, tab, cnt, n_zero, pm, d->q_pos);
     int rc = check_launch("rope_append_kernel");
     if (rc) return rc;
+    appended = true;
+  } else if (cnt) {
+    QW_CUDA(cudaMemsetAsync(cnt, 0, cnt_bytes, st));
   }
   if (use_umma) {
     PrefillCall pc;
@@ -384,19 +453,20 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
     pc.q = d->q; pc.gate = (d->flags & QW_F_GATE) ? d->gate : nullptr; pc.out = d->out;
     pc.out_is_f32 = (d->flags & QW_F_OUT_F32) != 0; pc.lse = d->lse;
     pc.kc = d->kc; pc.vc = d->vc; pc.cache_rows = d->cache_rows; pc.cache_row = d->cache_row; pc.pages = pm;
-    pc.pos = d->pos; pc.mpos = d->mpos; pc.n_seq = d->n_seq; pc.n_new = d->n_new;
+    pc.pos = d->pos; pc.q_pos = d->q_pos; pc.mpos = d->mpos; pc.n_seq = d->n_seq; pc.n_new = d->n_new;
     pc.q_heads = d->q_heads; pc.kv_heads = d->kv_heads; pc.scale = d->scale;
     pc.do_rope = (d->flags & QW_F_ROPE) != 0; pc.status = d->status;
     pc.rope = tab;
     pc.fast_p = (d->flags & QW_F_FAST_P) ? 1 : 0;
     int n = 0;
+    g_attn_kernel = "prefill_umma_pair_kernel";
     prof_mark(0, st);
-    int rc = (d->flags & QW_F_UMMA_1CTA) ? launch_prefill_umma(pc, st, &n) : launch_prefill_umma_pair(pc, st, &n);
+    int rc = launch_prefill_umma_pair(pc, st, &n);
     prof_mark(1, st);
     g_launches += n;
     if (rc == QW_ERR_CUDA) {
       cudaError_t e = cudaGetLastError();
-      return cuda_fail(e, "prefill_umma_kernel");
+      return cuda_fail(e, "prefill_umma_pair_kernel");
     }
     return rc;
   }
@@ -405,39 +475,79 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
   c.q = d->q; c.q_is_f32 = false; c.gate = d->gate; c.out = d->out;
   c.out_is_f32 = (d->flags & QW_F_OUT_F32) != 0; c.lse = d->lse; c.partial_out = partial;
   c.kc = d->kc; c.vc = d->vc; c.cache_rows = d->cache_rows; c.cache_row = d->cache_row; c.pages = pm;
-  c.pos = d->pos; c.mpos = d->mpos; c.n_seq = d->n_seq; c.n_new = d->n_new;
+  c.pos = d->pos; c.q_pos = d->q_pos; c.mpos = d->mpos; c.n_seq = d->n_seq; c.n_new = d->n_new;
   c.q_heads = d->q_heads; c.kv_heads = d->kv_heads; c.theta = d->theta; c.scale = d->scale;
   c.do_rope = (d->flags & QW_F_ROPE) != 0; c.do_gate = (d->flags & QW_F_GATE) != 0;
   c.no_causal = (d->flags & QW_F_NO_CAUSAL) != 0;
   c.q_dep = fr != nullptr;
-  if (!d->workspace || (reinterpret_cast<uintptr_t>(d->workspace) & 15) || d->workspace_bytes <= cnt_bytes)
-    return QW_ERR_WORKSPACE;
-  c.ws = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(d->workspace) + cnt_bytes);
-  c.ws_floats = (d->workspace_bytes - cnt_bytes) / sizeof(float);
+  c.pdl = appended;
+  c.ws = ws;
+  c.ws_floats = ws_floats;
   c.cnt = cnt;
   c.status = d->status;
-  if (cnt && !(d->flags & QW_F_NO_UMMA) && splitkv_umma_usable(d->n_new) && prefer_umma_decode(d->n_new))
-    return launch_splitkv_umma_call(c, st);
-  return launch_splitkv(c, st);
+  return sp.umma ? launch_splitkv_umma_call(c, st) : launch_splitkv(c, st);
 }
 
-// Drop-in attention launchers share this: one sequence, rows already rotated and appended.
+// Drop-in attention launchers share this: one sequence, rows already rotated and appended
+// (src/model.cu:228-236, src/prefill.cu:142-152 of the reference run rope and k_kv_append first).
+//   chunks of >= 64 rows      tcgen05 CTA-pair prefill kernel (an fp32 q is first copied to bf16 in scratch)
+//   2..63 rows, bf16          tcgen05 split-KV kernel
+//   1 row, and fp32 < 64 rows mma.sync split-KV kernel (fp32 q kept exact as bf16 hi + lo)
+// Split-KV arrival counters sit at the head of the scratch and are cleared by a memset node in front of
+// the kernel, which is legal inside a stream capture.
 template <typename T>
 int attn_dropin(const T *q, const qw_bf16 *kc, const qw_bf16 *vc, T *out, const int *dpos, int dim, int kv_heads,
                 int q_heads, float scale, float *scratch, int ctx, int rows, bool decode, cudaStream_t st) {
+  constexpr bool F32 = sizeof(T) == 4;
   g_launches = 0;
+  g_attn_kernel = "";
   if (!q || !kc || !vc || !out || !dpos || !scratch || ctx <= 0 || rows < 0) return QW_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(scratch) & 15) return QW_ERR_ARG;
   if (!geometry_ok(dim, kv_heads, q_heads)) return QW_ERR_SHAPE;
   if (decode && rows > 8) return QW_ERR_SHAPE;
   if (rows == 0) return QW_OK;
+  const size_t have = decode ? qw_attn_decode_scratch_floats(q_heads, kv_heads, ctx, rows)
+                             : qw_attn_prefill_scratch_floats(q_heads, kv_heads, ctx, rows);
+  if (!decode && prefill_umma_supported(rows)) {
+    const uint16_t *qb = reinterpret_cast<const uint16_t *>(q);
+    if (F32) {
+      const long long n = (long long)rows * q_heads * HEAD_DIM;
+      to_bf16_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const float *>(q),
+                                                                     reinterpret_cast<uint16_t *>(scratch), n);
+      int rc = check_launch("to_bf16_kernel");
+      if (rc) return rc;
+      qb = reinterpret_cast<const uint16_t *>(scratch);
+    }
+    PrefillCall pc;
+    memset(&pc, 0, sizeof(pc));
+    pc.q = qb; pc.out = out; pc.out_is_f32 = F32;
+    pc.kc = kc; pc.vc = vc; pc.cache_rows = ctx; pc.pos = dpos;
+    pc.n_seq = 1; pc.n_new = rows; pc.q_heads = q_heads; pc.kv_heads = kv_heads; pc.scale = scale;
+    pc.rope = make_rope_table(1e7f, ROTARY_DIM);  // unused: q arrives rotated
+    int n = 0;
+    g_attn_kernel = "prefill_umma_pair_kernel";
+    prof_mark(0, st);
+    int rc = launch_prefill_umma_pair(pc, st, &n);
+    prof_mark(1, st);
+    g_launches += n;
+    if (rc == QW_ERR_CUDA) return cuda_fail(cudaGetLastError(), "prefill_umma_pair_kernel");
+    return rc;
+  }
+  const SplitPlan sp = split_plan(1, rows, kv_heads, !F32);
+  const size_t cnt_bytes = mixer_cnt_bytes(1, rows, kv_heads);
+  if (have * sizeof(float) <= cnt_bytes) return QW_ERR_WORKSPACE;
   AttnCall c;
   memset(&c, 0, sizeof(c));
-  c.q = q; c.q_is_f32 = sizeof(T) == 4; c.out = out; c.out_is_f32 = sizeof(T) == 4;
+  c.q = q; c.q_is_f32 = F32; c.out = out; c.out_is_f32 = F32;
   c.kc = kc; c.vc = vc; c.cache_rows = ctx; c.pos = dpos;
   c.n_seq = 1; c.n_new = rows; c.q_heads = q_heads; c.kv_heads = kv_heads;
-  c.theta = 1e7f; c.scale = scale; c.ws = scratch;
-  c.ws_floats = decode ? (size_t)rows * q_heads * ctx : qw_attn_prefill_scratch_floats(q_heads, kv_heads, ctx, rows);
-  return launch_splitkv(c, st);
+  c.theta = 1e7f; c.scale = scale;
+  c.cnt = reinterpret_cast<int *>(scratch);
+  c.ws = scratch + cnt_bytes / sizeof(float);
+  c.ws_floats = have - cnt_bytes / sizeof(float);
+  if ((long long)(c.ws_floats / sp.slot) - sp.units < 1) return QW_ERR_WORKSPACE;
+  QW_CUDA(cudaMemsetAsync(c.cnt, 0, cnt_bytes, st));
+  return sp.umma ? launch_splitkv_umma_call(c, st) : launch_splitkv(c, st);
 }
 
 // ---- allocation-free decode: split-KV partials in a fixed array inside the library image --------
@@ -452,10 +562,10 @@ static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS]
 // could use.  The device address is looked up once per device, with that device current.
 int noalloc_scratch_address(float **out) {
   static std::mutex mu;
-  static float *addr[64] = {nullptr};
+  static float *addr[MAX_DEVICES] = {nullptr};
   int dev = 0;
   QW_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return QW_ERR_ARG;
+  if (dev < 0 || dev >= MAX_DEVICES) return QW_ERR_ARG;
   std::lock_guard<std::mutex> lock(mu);
   if (!addr[dev]) {
     void *p = nullptr;
@@ -469,12 +579,6 @@ int noalloc_scratch_address(float **out) {
 
 }  // namespace
 
-#ifdef QWB_TIMELINE
-extern "C" void qw_debug_set_timeline(unsigned long long *buf, int block) {
-  qwb::g_timeline_buf = buf;
-  qwb::g_timeline_block = block;
-}
-#endif
 
 extern "C" {
 
@@ -490,23 +594,21 @@ const char *qw_strerror(int code) {
     default: return "unknown error code";
   }
 }
-int qw_abi_version(void) { return 2; }
+int qw_abi_version(void) { return 3; }
 const char *qw_last_cuda_error(void) { return g_cuda_err; }
 int qw_last_launch_count(void) { return g_launches; }
+const char *qw_last_attention_kernel(void) { return g_attn_kernel; }
 
 int qw_profile_enable(int on) {
-  if (on && !g_prof_ev[0]) {
-    QW_CUDA(cudaEventCreate(&g_prof_ev[0]));
-    QW_CUDA(cudaEventCreate(&g_prof_ev[1]));
-  }
   g_prof_on = on != 0;
-  g_prof_valid = false;
+  g_prof_dev = -1;
+  g_prof_open = false;
   return QW_OK;
 }
 int qw_profile_last_kernel_ms(float *ms) {
-  if (!ms || !g_prof_valid) return QW_ERR_ARG;
-  QW_CUDA(cudaEventSynchronize(g_prof_ev[1]));
-  QW_CUDA(cudaEventElapsedTime(ms, g_prof_ev[0], g_prof_ev[1]));
+  if (!ms || g_prof_dev < 0) return QW_ERR_ARG;
+  QW_CUDA(cudaEventSynchronize(g_prof_ev[g_prof_dev][1]));
+  QW_CUDA(cudaEventElapsedTime(ms, g_prof_ev[g_prof_dev][0], g_prof_ev[g_prof_dev][1]));
   return QW_OK;
 }
 
@@ -570,17 +672,15 @@ int qw_gate_sigmoid_f32(float *x, const float *gate, int n, qw_stream stream) {
 }
 
 size_t qw_attn_decode_scratch_floats(int q_heads, int kv_heads, int ctx, int B) {
-  (void)q_heads; (void)ctx;
-  if (B <= 0 || kv_heads <= 0) return 0;
-  // one CTA slot plus one slot per unit is the minimum; more slots allow more CTAs
-  const int rb = splitkv_rb(B);
-  const int nblk = (B + rb - 1) / rb;
-  return (size_t)(1 + nblk * kv_heads) * splitkv_slot_floats(rb);
+  (void)kv_heads;
+  if (B <= 0 || q_heads <= 0 || ctx <= 0) return 0;
+  return (size_t)B * q_heads * ctx;  // the reference kernel's own need at the same launch; all of it is used
 }
 size_t qw_attn_prefill_scratch_floats(int q_heads, int kv_heads, int ctx, int T) {
-  (void)q_heads; (void)ctx;
-  if (T <= 0 || kv_heads <= 0) return 0;
-  return splitkv_ws_floats(1, T, kv_heads);
+  (void)ctx;
+  if (T <= 0 || kv_heads <= 0 || q_heads <= 0) return 0;
+  if (prefill_umma_supported(T)) return (size_t)T * q_heads * (HEAD_DIM / 2);  // bf16 copy of an fp32 q
+  return mixer_cnt_bytes(1, T, kv_heads) / sizeof(float) + mixer_slot_floats(1, T, kv_heads);
 }
 
 int qw_attn_decode_bf16(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out, const int *dpos,

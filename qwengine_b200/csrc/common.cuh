@@ -168,18 +168,6 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// Timeline probe for kernel tuning; compiled in only with -DQWB_TIMELINE (never in the product build).
-#ifdef QWB_TIMELINE
-#define QWB_TL(ev, j) do { if (p.dbg && (int)blockIdx.x == p.dbg_block && (j) < 64) p.dbg[(ev) * 64 + (j)] = ((ev) == 30 || (ev) == 31) ? global_timer_ns() : (unsigned long long)clock64(); } while (0)
-#define QWB_TLB(k) do { if (p.dbg && p.dbg_block < 0) p.dbg[2048 + 2 * blockIdx.x + (k)] = global_timer_ns(); } while (0)
-#define QWB_TLV(ev, j, val) do { if (p.dbg && (int)blockIdx.x == p.dbg_block && (j) < 64) p.dbg[(ev) * 64 + (j)] = (unsigned long long)(val); } while (0)
-extern unsigned long long *g_timeline_buf;
-extern int g_timeline_block;
-#else
-#define QWB_TL(ev, j) do { } while (0)
-#define QWB_TLV(ev, j, val) do { } while (0)
-#define QWB_TLB(k) do { } while (0)
-#endif
 // Bounded wait: a short spin, then polling against the wall clock.  After WAIT_LIMIT_NS the
 // wait gives up and returns false; the caller records an error code and unwinds without
 // waiting again, so a lost signal costs a fraction of a second, not the GPU.

@@ -51,6 +51,16 @@ __global__ void __launch_bounds__(256) gate_sigmoid_kernel(T *x, const T *gate, 
   store8<T>(x + i, a);
 }
 
+// dst[i] = bf16(src[i]), round to nearest even; 8 elements per thread, n % 8 == 0.  Stages an fp32 q for the
+// tcgen05 prefill kernel behind the fp32 drop-in launcher.
+__global__ void __launch_bounds__(256) to_bf16_kernel(const float *src, uint16_t *dst, long long n) {
+  const long long i = ((long long)blockIdx.x * 256 + threadIdx.x) * 8;
+  if (i >= n) return;
+  float x[8];
+  load8<float>(src + i, x);
+  store8<uint16_t>(dst + i, x);
+}
+
 // Fused rope(k) + append for a batch: one block per new token row, kv_heads * 32 threads,
 // thread = one 8-channel group of one head.  The 32 (cos, sin) pairs of the row's position
 // are computed once in double and shared by all heads.
@@ -58,7 +68,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const uint16_t *k_new,
                                                           uint16_t *vc, const int *pos, const int64_t *cache_row,
                                                           const int *mpos, int n_new, int kv_heads, int do_rope,
                                                           const __grid_constant__ RopeTable tab, int *zero_ints,
-                                                          int n_zero, PageMap pages) {
+                                                          int n_zero, PageMap pages, const int *q_pos) {
   grid_dep_launch_dependents();  // the attention launch behind this one may start now; it waits where it must
   // block 0 also clears the split-KV arrival counters of the attention launch that follows
   if (blockIdx.x == 0)
@@ -69,7 +79,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const uint16_t *k_new,
   const int pz = pos[s] + b;
   if (do_rope && threadIdx.x < ROT_PAIRS) {
     const int i = threadIdx.x;
-    const int pp = mpos ? mpos[r * 3 + mrope_component(i)] : pz;
+    const int pp = mpos ? mpos[r * 3 + mrope_component(i)] : (q_pos ? q_pos[s] + b : pz);
     rope_sincos_exact(pp, tab.inv_freq[i], cs[i][0], cs[i][1]);
   }
   __syncthreads();
@@ -115,7 +125,7 @@ __global__ void __launch_bounds__(256) fused_rows_kernel(const TIn *fused, const
                                                          const int64_t *cache_row, const int *mpos, int n_new,
                                                          int q_heads, int kv_heads, int do_rope,
                                                          const __grid_constant__ RopeTable tab, int *zero_ints,
-                                                         int n_zero, PageMap pages) {
+                                                         int n_zero, PageMap pages, const int *q_pos) {
   grid_dep_launch_dependents();  // the attention launch behind this one may start now; it waits where it must
   if (blockIdx.x == 0 && blockIdx.y == 0)
     for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero_ints[i] = 0;
@@ -160,7 +170,7 @@ __global__ void __launch_bounds__(256) fused_rows_kernel(const TIn *fused, const
   load8<uint16_t>(k_norm_w + lane * 8, w8);
   double cs = 1.0, sn = 0.0;  // lane i: cos / sin of rotary pair i
   if (do_rope) {
-    const int pp = mpos ? mpos[r * 3 + mrope_component(lane)] : pz;
+    const int pp = mpos ? mpos[r * 3 + mrope_component(lane)] : (q_pos ? q_pos[s] + b : pz);
     rope_sincos_exact(pp, tab.inv_freq[lane], cs, sn);
   }
   double ss = 0.0;

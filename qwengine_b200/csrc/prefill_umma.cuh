@@ -1,4 +1,4 @@
-// Causal chunked-prefill attention on tcgen05 / TMEM (interface; kernel in prefill_umma.cu).
+// Causal chunked-prefill attention on tcgen05 / TMEM (interface; kernel in prefill_umma2.cu).
 #pragma once
 
 #include "common.cuh"
@@ -16,6 +16,7 @@ struct PrefillCall {
   const int64_t *cache_row;
   qwb::PageMap pages;   // block table, if the cache is paged
   const int *pos;
+  const int *q_pos;     // null, or the absolute position of each sequence's first new row (RoPE angles)
   const int *mpos;
   int n_seq, n_new, q_heads, kv_heads;
   float scale;
@@ -27,9 +28,8 @@ struct PrefillCall {
 
 // True when the tcgen05 kernel takes a chunk of n_new rows (shorter chunks go to split-KV).
 bool prefill_umma_supported(int n_new);
-// Launches the kernel(s); *n_launched receives how many.  Returns a QW_* code.
-int launch_prefill_umma(const PrefillCall &c, cudaStream_t st, int *n_launched);
-// Same contract, CTA-pair kernel (tcgen05 cta_group::2); needs an even number of query heads.
+// Launches the CTA-pair kernel (tcgen05 cta_group::2; needs an even number of query heads);
+// *n_launched receives how many kernels were launched.  Returns a QW_* code.
 int launch_prefill_umma_pair(const PrefillCall &c, cudaStream_t st, int *n_launched);
 
 }  // namespace qwb

@@ -9,8 +9,8 @@
 // and the same 128 KB ring now holds two tiles of look-ahead instead of one, which is what hides
 // the load latency the single-CTA kernel is bound by.
 //
-// Everything else follows the single-CTA kernel (prefill_umma.cu): TMEM map (O | S0 | S1, P over
-// S as bf16 hi + lo), warp roles (0 = TMA producer, 1 = TMEM owner and -- in the leader CTA only --
+// TMEM map: O | S0 | S1, P over
+// S as bf16 hi + lo; warp roles (0 = TMA producer, 1 = TMEM owner and -- in the leader CTA only --
 // MMA issuer, 2..17 = four softmax warpgroups), RoPE(q) prologue in shared memory, 1/l * sigmoid
 // epilogue out of TMEM, bounded waits with an abort flag and a status word.
 //
@@ -25,6 +25,7 @@
 //
 #include "prefill_umma.cuh"
 
+#include <atomic>
 #include <cstring>
 
 #include "umma_common.cuh"
@@ -176,7 +177,6 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
   const int kv_len = pos + q0 + rows_valid;
   const int nt = (kv_len + P2_BN - 1) / P2_BN;
 
-  if (tid == 64) QWB_TL(27, 0);
   if (tid == 0) {
     mbar_init(&ctl->q_full, 1);
     mbar_init(&ctl->q_ready, 2 * P2_SM_THREADS);
@@ -332,14 +332,11 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         if (j < nt) {
           // ---- S[j & 1] = Q K_j^T for both CTAs' rows ----
           const uint32_t d_s = tmem + ((j & 1) ? TMEM_S1 : TMEM_S0);
-          QWB_TL(0, j);
 #pragma unroll
           for (int i = 0; i < 2; ++i, ++it) {
             const int sl = it % P2_NSLOT;
-            QWB_TL(10 + i, j);
             ok = ok && wait_cluster_or_abort(&ctl->slot_full[sl], (it / P2_NSLOT) & 1, abort_flag);
             if (!ok) { fail(DEV_ERR_MMA_WAIT); break; }
-            QWB_TL(12 + i, j);
             tc_fence_after();
             const uint64_t kd = kdesc0 + (uint64_t)(sl * (P2_SLOT >> 4));
 #pragma unroll
@@ -360,23 +357,19 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
           // one completion point for the whole S tile, seen by the softmax warps (S is ready) and
           // by both producers (the tile's K slots are free)
           if (ok) umma_commit_both(&ctl->s_full[j & 1]);
-          QWB_TL(1, j);
         }
         if (j >= 1 && ok) {
           // ---- O += P_{j-1} V_{j-1} ----
           const int jj = j - 1;
           ok = wait_cluster_or_abort(&ctl->p_full[jj & 1], (jj >> 1) & 1, abort_flag);
           if (!ok) { fail(DEV_ERR_SOFTMAX_WAIT); break; }
-          QWB_TL(2, jj);
           tc_fence_after();
           const uint32_t a_p = tmem + ((jj & 1) ? TMEM_S1 : TMEM_S0);
 #pragma unroll
           for (int g = 0; g < 2; ++g, ++it) {
             const int sl = it % P2_NSLOT;
-            QWB_TL(14 + g * 2, jj);
             ok = ok && wait_cluster_or_abort(&ctl->slot_full[sl], (it / P2_NSLOT) & 1, abort_flag);
             if (!ok) { fail(DEV_ERR_MMA_WAIT); break; }
-            QWB_TL(15 + g * 2, jj);
             tc_fence_after();
             const uint64_t vd = vdesc0 + (uint64_t)(sl * (P2_SLOT >> 4));
 #pragma unroll
@@ -388,7 +381,6 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
             }
           }
           if (ok) umma_commit_both(&ctl->o_done[jj & 1]);  // O updated; the tile's V slots are free
-          QWB_TL(3, jj);
         }
       }
     }
@@ -397,12 +389,11 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
     const int wg = (warp - 2) >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const int qpos = pos + q0 + row;
+    const int qpos = pos + q0 + row;                                   // causal limit: keys 0 .. qpos
+    const int rope_pos = (p.q_pos ? p.q_pos[s] : pos) + q0 + row;    // RoPE angle
     const uint32_t q_ready_addr = map_to_cta(smem_u32(&ctl->q_ready), 0);
     const uint32_t p_full_addr[2] = {map_to_cta(smem_u32(&ctl->p_full[0]), 0), map_to_cta(smem_u32(&ctl->p_full[1]), 0)};
-    if (tid == 64) QWB_TL(27, 1);
     bool ok = wait_or_abort(&ctl->q_full, 0, abort_flag);
-    if (tid == 64) QWB_TL(28, 0);
     if (ok && p.do_rope) {
       const size_t trow = (size_t)s * p.n_new + q0 + row;
       const bool live = row < rows_valid;
@@ -422,7 +413,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
           const int i = c * 8 + w2 * 2 + e;
           const float x = e ? bf16hi(xw[w2]) : bf16lo(xw[w2]);
           const float y = e ? bf16hi(yw[w2]) : bf16lo(yw[w2]);
-          const int pz = (p.mpos && live) ? p.mpos[trow * 3 + mrope_component(i)] : qpos;
+          const int pz = (p.mpos && live) ? p.mpos[trow * 3 + mrope_component(i)] : rope_pos;
           float cs, sn;
           rope_sincos_reduced(pz, p.rope.inv_freq[i], cs, sn);
           xr[e] = x * cs - y * sn;
@@ -440,7 +431,6 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
     }
     fence_proxy_async();
     remote_arrive_release(q_ready_addr);
-    if (tid == 64) QWB_TL(29, 0);
 
     float m_used = -INFINITY, l_run = 0.f;
     int o_seen = 0;  // P V completions observed so far, in order (tile t: o_done[t & 1], phase t / 2)
@@ -452,14 +442,11 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
     };
     for (int j = 0; j < nt; ++j) {
       const uint32_t t_s = tmem + lane_sel + ((j & 1) ? TMEM_S1 : TMEM_S0);
-      if (tid == 64) QWB_TL(4, j);
       if (ok) ok = wait_or_abort(&ctl->s_full[j & 1], (j >> 1) & 1, abort_flag);
-      if (tid == 64) QWB_TL(5, j);
       tc_fence_after();
       uint32_t sr[32];
       tmem_ld32(t_s + wg * 32, sr);
       tmem_wait_ld();
-      if (tid == 64) QWB_TL(6, j);
       const int key0 = j * P2_BN + wg * 32;
       const bool need_mask = j * P2_BN + P2_BN - 1 > pos + q0;
       float mx = -INFINITY;
@@ -477,7 +464,6 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
       }
       ctl->mxbuf[j & 1][wg][row] = mx;
       asm volatile("bar.sync 1, %0;" ::"n"(P2_SM_THREADS) : "memory");
-      if (tid == 64) QWB_TL(7, j);
 #pragma unroll
       for (int w2 = 0; w2 < P2_NWG; ++w2) mx = fmaxf(mx, ctl->mxbuf[j & 1][w2][row]);
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
@@ -503,7 +489,6 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         }
         m_used = m_new;
       }
-      if (tid == 64) QWB_TL(24, j);
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
       float lsum = 0.f;
       uint32_t hi[16], lo[16];
@@ -517,28 +502,21 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         lo[i >> 1] = pack_bf16(p0 - bf16lo(h), p1 - bf16hi(h));
       }
       l_run += lsum;
-      if (tid == 64) QWB_TL(25, j);
       tmem_st16(t_s + wg * 16, hi);
       if (!p.fast_p) tmem_st16(t_s + 64 + wg * 16, lo);
       tmem_wait_st();
-      if (tid == 64) QWB_TL(26, j);
       tc_fence_before();
       remote_arrive(p_full_addr[j & 1]);
-      if (tid == 64) QWB_TL(8, j);
       if (j > 0) wait_pv_done(j - 1);
-      if (tid == 64) QWB_TL(9, j);
     }
 
-    if (tid == 64) QWB_TL(18, 0);
     ctl->lbuf[wg][row] = l_run;
     wait_pv_done(nt - 1);
-    if (tid == 64) QWB_TL(18, 1);
     asm volatile("bar.sync 1, %0;" ::"n"(P2_SM_THREADS) : "memory");
     if (!__all_sync(0xffffffffu, ok)) {
       if (lane == 0 && !*abort_flag && p.status) *p.status = DEV_ERR_SOFTMAX_WAIT;
       *abort_flag = 1;
     } else {
-      if (tid == 64) QWB_TL(18, 2);
       tc_fence_after();
       float l_tot = 0.f;
 #pragma unroll
@@ -556,7 +534,6 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
       const int nrows = min(32, rows_valid - row0);
       const size_t elem0 = (((size_t)s * p.n_new + q0 + row0) * p.q_heads + head) * HEAD_DIM + wg * 64 + 2 * lane;
       const size_t row_stride = (size_t)p.q_heads * HEAD_DIM;
-      if (tid == 64) QWB_TL(18, 3);
       uint32_t gw[32];
       {
         const uint16_t *gp = p.gate ? p.gate + elem0 : nullptr;
@@ -566,7 +543,6 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
           gp += gp ? row_stride : 0;
         }
       }
-      if (tid == 64) QWB_TL(18, 4);
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t orow[32];
@@ -576,7 +552,6 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         for (int i = 0; i < 32; ++i) stage[lane * 65 + c * 32 + i] = __uint_as_float(orow[i]) * inv;
       }
       __syncwarp();
-      if (tid == 64) QWB_TL(18, 5);
       if (p.out_is_f32) {
         float *op = reinterpret_cast<float *>(p.out) + elem0;
 #pragma unroll
@@ -598,12 +573,10 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
           }
         }
       }
-      if (tid == 64) QWB_TL(18, 6);
       if (wg == 0 && row < rows_valid && p.lse) p.lse[grow] = (m_used + log2f(l_tot)) * LN2;
     }
   }
 
-  if (tid == 64) QWB_TL(19, 0);
   // ---- teardown: both CTAs meet (no signal may target a CTA that has left), then free TMEM ----
   tc_fence_before();
   __syncthreads();
@@ -620,6 +593,8 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
 
 }  // namespace
 
+bool prefill_umma_supported(int n_new) { return n_new >= 64; }
+
 int launch_prefill_umma_pair(const PrefillCall &c, cudaStream_t st, int *n_launched) {
   *n_launched = 0;
   if ((reinterpret_cast<uintptr_t>(c.q) | reinterpret_cast<uintptr_t>(c.kc) | reinterpret_cast<uintptr_t>(c.vc)) & 15)
@@ -627,29 +602,27 @@ int launch_prefill_umma_pair(const PrefillCall &c, cudaStream_t st, int *n_launc
   if (c.q_heads % 2) return 2;
   PrefillParams p;
   memset(&p, 0, sizeof(p));
-  p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.cache_row = c.cache_row; p.pages = c.pages; p.pos = c.pos; p.mpos = c.mpos;
+  p.gate = c.gate; p.out = c.out; p.lse = c.lse; p.cache_row = c.cache_row; p.pages = c.pages; p.pos = c.pos; p.q_pos = c.q_pos; p.mpos = c.mpos;
   p.status = c.status; p.n_seq = c.n_seq; p.n_new = c.n_new; p.q_heads = c.q_heads; p.kv_heads = c.kv_heads;
   p.n_qtiles = (c.n_new + P2_BM - 1) / P2_BM;
   p.scale_log2 = c.scale * LOG2E;
   p.do_rope = c.do_rope; p.out_is_f32 = c.out_is_f32;
   p.fast_p = c.fast_p;
   p.rope = c.rope;
-#ifdef QWB_TIMELINE
-  p.dbg = g_timeline_buf; p.dbg_block = g_timeline_block;
-#endif
   CUtensorMap mq, mk, mv;
   if (encode_map(&mq, c.q, (int64_t)c.n_seq * c.n_new, c.q_heads * HEAD_DIM, P2_BM) != CUDA_SUCCESS) return 3;
   if (encode_map(&mk, c.kc, c.cache_rows, c.kv_heads * HEAD_DIM, 64) != CUDA_SUCCESS) return 3;
   if (encode_map(&mv, c.vc, c.cache_rows, c.kv_heads * HEAD_DIM, 64) != CUDA_SUCCESS) return 3;
   constexpr size_t smem = 1024 + P2_QBYTES + P2_NSLOT * P2_SLOT + sizeof(PairCtl);
-  static bool configured[64] = {false};
+  // once per device; the step is idempotent, so an atomic flag is all that concurrent host threads need
+  static std::atomic<int> configured[64];
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  if (dev < 0 || !configured[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(prefill_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return 3;
-    configured[dev] = true;
+    if (dev >= 0) configured[dev].store(1, std::memory_order_release);
   }
   const long long grid = (long long)c.n_seq * p.n_qtiles * c.q_heads;  // CTAs; two per cluster
   if (grid > 0x7fffffffll) return 2;

@@ -36,6 +36,7 @@ struct SplitKVParams {
   float *lse;             // [n_seq][n_new][q_heads] or null
   float *partial_out;     // non-null: emit (o, m, l) per (row, head) instead of out / lse
   const int *pos;         // [n_seq]
+  const int *q_pos;       // [n_seq] or null: absolute position of a sequence's first new row (RoPE angles) when it is not pos[s]
   const int64_t *cache_row;  // [n_seq] or null
   PageMap pages;             // block table, if the cache is paged
   const int *mpos;        // [n_seq][n_new][3] or null
@@ -51,8 +52,6 @@ struct SplitKVParams {
   int do_rope, do_gate;
   int q_rows_pad;         // tcgen05 kernel: rows of the Q tile that really exist in shared memory (32, 64 or 128)
   int nslot;              // tcgen05 kernel: 16 KB ring slots that fit beside that Q tile
-  unsigned long long *dbg;  // timeline probe (only written when built with QWB_TIMELINE)
-  int dbg_block;
   int q_dep;              // q and gate are written by the launch before this one (fused projection rows)
   int no_causal;          // every row sees exactly pos[s] keys (a KV sub-range without the new rows)
   RopeTable rope;
@@ -62,6 +61,7 @@ struct UnitInfo {
   int s, blk, kvh;
   int tok0, ntok;   // first new-token index of the block and tokens in it
   int pos;          // tokens cached before the call for this sequence
+  int rpos;         // position of the sequence's first new row for the RoPE angles (pos unless q_pos is given)
   int len;          // keys visible to the last row of the unit
 };
 
@@ -74,6 +74,7 @@ __device__ __forceinline__ UnitInfo unit_info(const SplitKVParams &p, int u) {
   ui.tok0 = ui.blk * p.rb;
   ui.ntok = min(p.rb, p.n_new - ui.tok0);
   ui.pos = p.pos[ui.s];
+  ui.rpos = p.q_pos ? p.q_pos[ui.s] : ui.pos;
   ui.len = p.no_causal ? ui.pos : ui.pos + ui.tok0 + ui.ntok;
   return ui;
 }
@@ -226,9 +227,6 @@ __device__ __forceinline__ void merge_unit_row(const SplitKVParams &p, int u, co
   // running maximum, strictly in CTA order.
   float mg = -INFINITY, lg = 0.f;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#ifdef QWB_TIMELINE
-  long long tl0 = clock64(); int tlb = 0;
-#endif
   for (int c0 = c_first; c0 <= c_last; c0 += 4) {
     float mv[4], lv[4];
     float4 av[4], bv[4];
@@ -257,17 +255,8 @@ __device__ __forceinline__ void merge_unit_row(const SplitKVParams &p, int u, co
       acc[4] = acc[4] * f_old + bv[k].x * f; acc[5] = acc[5] * f_old + bv[k].y * f;
       acc[6] = acc[6] * f_old + bv[k].z * f; acc[7] = acc[7] * f_old + bv[k].w * f;
     }
-#ifdef QWB_TIMELINE
-    if (p.dbg && (int)blockIdx.x == p.dbg_block && threadIdx.x == 64 && tlb < 8) { p.dbg[28 * 64 + 8 * (row >= 16) + tlb] = clock64() - tl0 + (acc[0] == 12345.f); ++tlb; }
-#endif
   }
-#ifdef QWB_TIMELINE
-  if (p.dbg && (int)blockIdx.x == p.dbg_block && threadIdx.x == 64) p.dbg[28 * 64 + 16 + (row >= 16)] = clock64() - tl0;
-#endif
   merge_finish<TOut>(p, ui, row, lane, mg, lg, acc);
-#ifdef QWB_TIMELINE
-  if (p.dbg && (int)blockIdx.x == p.dbg_block && threadIdx.x == 64) p.dbg[28 * 64 + 18 + (row >= 16)] = clock64() - tl0;
-#endif
 }
 
 // FOLD = false: a dedicated producer warp (warp NCW).  FOLD = true: lane 0 of consumer warp 0 also
@@ -302,7 +291,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
   const int cta = blockIdx.x;
-  if (tid == 0) { QWB_TLB(0); QWB_TL(30, 0); }
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], NCW); }
@@ -320,7 +308,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   __syncthreads();
   const long long total = seg[0];
   const int G = (int)(seg[2] >> 32);                  // CTAs in use (the rest of the grid leaves here)
-  if (tid == 0) QWB_TL(30, 1);
   const long long g0 = cta < G ? total * cta / G : 0, g1 = cta < G ? total * (cta + 1) / G : 0;
   if (g0 >= g1) return;  // uniform for the whole CTA
 
@@ -395,8 +382,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   uint32_t it = 0;
   int u = (int)(seg[2] & 0xffffffffll);
   long long pre = seg[1];
-  int segx = 0;  // segments done (timeline probe only)
-  (void)segx;
   const uint32_t qhi_s = smem_u32(qregion);
   // Per-lane ldmatrix addresses.  The swizzle XORs the 16-byte column (d / 8) & 7 with row & 7,
   // so for a fixed lane only four distinct column offsets occur; the rest is a constant stride.
@@ -433,37 +418,37 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     constexpr int QIT = (ROWS * 32 + NCT - 1) / NCT;
     float xq[QIT][8], rx[QIT], ry[QIT];
 #pragma unroll
-    for (int it = 0; it < QIT; ++it) {
-      const int idx = tid + it * NCT;
+    for (int qi = 0; qi < QIT; ++qi) {
+      const int idx = tid + qi * NCT;
       const int row = idx >> 5, c16 = idx & 31;  // 8 channels d = c16*8 .. +7
 #pragma unroll
-      for (int j = 0; j < 8; ++j) xq[it][j] = 0.f;
+      for (int j = 0; j < 8; ++j) xq[qi][j] = 0.f;
       if (idx < ROWS * 32 && row < R && !(p.do_rope && c16 < 8)) {
         const int b = row / GROUP, hh = row % GROUP;
         const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
-        load8<TIn>(reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM + c16 * 8, xq[it]);
+        load8<TIn>(reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM + c16 * 8, xq[qi]);
       }
-      rx[it] = ry[it] = 0.f;
+      rx[qi] = ry[qi] = 0.f;
       if (p.do_rope && idx < ROWS * ROT_PAIRS) {
         const int rrow = idx / ROT_PAIRS, i = idx % ROT_PAIRS;  // pair (i, i + 32) of this row
         if (rrow < R) {
           const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + rrow / GROUP) * p.q_heads + (size_t)ui.kvh * GROUP + rrow % GROUP;
           const TIn *src = reinterpret_cast<const TIn *>(p.q) + grow * HEAD_DIM;
-          rx[it] = load_as_f32<TIn>(src + i);
-          ry[it] = load_as_f32<TIn>(src + i + ROT_PAIRS);
+          rx[qi] = load_as_f32<TIn>(src + i);
+          ry[qi] = load_as_f32<TIn>(src + i + ROT_PAIRS);
         }
       }
     }
 #pragma unroll
-    for (int it = 0; it < QIT; ++it) {
-      const int idx = tid + it * NCT;
+    for (int qi = 0; qi < QIT; ++qi) {
+      const int idx = tid + qi * NCT;
       const int row = idx >> 5, c16 = idx & 31;
       if (idx >= ROWS * 32 || (p.do_rope && c16 < 8)) continue;  // rotary channels are written pair-wise below
       uint32_t hi[4], lo[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        hi[j] = pack_bf16(xq[it][2 * j], xq[it][2 * j + 1]);
-        lo[j] = pack_bf16(xq[it][2 * j] - bf16lo(hi[j]), xq[it][2 * j + 1] - bf16hi(hi[j]));
+        hi[j] = pack_bf16(xq[qi][2 * j], xq[qi][2 * j + 1]);
+        lo[j] = pack_bf16(xq[qi][2 * j] - bf16lo(hi[j]), xq[qi][2 * j + 1] - bf16hi(hi[j]));
       }
       *reinterpret_cast<uint4 *>(qregion + q_hi_off(row, c16 * 8)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
       if (c16 * 8 < p.q_lo_dims)
@@ -472,18 +457,18 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     }
     if (p.do_rope) {
 #pragma unroll
-      for (int it = 0; it < QIT; ++it) {
-        const int idx = tid + it * NCT;
+      for (int qi = 0; qi < QIT; ++qi) {
+        const int idx = tid + qi * NCT;
         if (idx >= ROWS * ROT_PAIRS) continue;
         const int row = idx / ROT_PAIRS, i = idx % ROT_PAIRS;
         float xr = 0.f, yr = 0.f;
         if (row < R) {
           const size_t trow = (size_t)ui.s * p.n_new + ui.tok0 + row / GROUP;
-          const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.pos + ui.tok0 + row / GROUP;
+          const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.rpos + ui.tok0 + row / GROUP;
           float c, sn;
           rope_sincos_reduced(pz, p.rope.inv_freq[i], c, sn);  // angle reduced in double, then the fast sincos
-          xr = rx[it] * c - ry[it] * sn;
-          yr = rx[it] * sn + ry[it] * c;
+          xr = rx[qi] * c - ry[qi] * sn;
+          yr = rx[qi] * sn + ry[qi] * c;
         }
         const uint16_t xh = f32_to_bf16_bits(xr), yh = f32_to_bf16_bits(yr);
         *reinterpret_cast<uint16_t *>(qregion + q_hi_off(row, i)) = xh;
@@ -497,7 +482,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       }
     }
     consumer_sync(NCT);
-    if (tid == 0) QWB_TL(30, 2 + 8 * segx);
     uint32_t qf[QREG ? 16 : 1][4], qlf[QREG && LOK > 0 ? LOK : 1][4];
     if (QREG) {
 #pragma unroll
@@ -663,7 +647,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       if (lane == 0) mbar_arrive(&empty[st]);
     }
 
-    if (tid == 0) QWB_TL(30, 9 + 8 * segx);
     // ---- merge the SK_KS key-slice warps of each channel group, in slice order ----
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -679,7 +662,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         }
       }
     consumer_sync(NCT);  // also: every warp is past its last tile, the Q area may be reused
-    if (tid == 0) QWB_TL(30, 3 + 8 * segx);
     float *comb = reinterpret_cast<float *>(qregion);  // [ROWS][256] fp32, 8-float groups XOR (row & 7)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -694,7 +676,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
 #pragma unroll
         for (int n = 0; n < NT_O; ++n) { o[mt][n][2 * h2] *= f; o[mt][n][2 * h2 + 1] *= f; }
       }
-    if (tid == 0) QWB_TL(30, 7 + 8 * segx);
     for (int k = 0; k < SK_KS; ++k) {
       if (ks == k) {
         // all loads of the round first, then all stores: read-add-write per element would serialise on
@@ -730,7 +711,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       consumer_sync(NCT);
     }
 
-    if (tid == 0) QWB_TL(30, 8 + 8 * segx);
     // ---- finish the segment: final output, or a partial for the merge kernel ----
     for (int idx = tid; idx < R * 32; idx += NCT) {
       const int row = idx >> 5, c8 = idx & 31;  // channels c8*8 .. +7
@@ -771,7 +751,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         if (c8 == 0) { dst[256] = mg; dst[257] = lg; }
       }
     }
-    if (tid == 0) QWB_TL(30, 4 + 8 * segx);
     // ---- with arrival counters: the CTA that completes a unit last merges it right here ----
     if (!whole && p.cnt) {
       // Release: the barrier orders every thread's partial stores before thread 0's fence, which is cumulative,
@@ -785,7 +764,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         __threadfence();
       }
       consumer_sync(NCT);
-      if (tid == 0) QWB_TL(30, 5 + 8 * segx);
       const int c_first = cta_of_tile(pre, total, G), c_last = cta_of_tile(pre + nt_unit - 1, total, G);
       int nparts = 0;
       for (int c = c_first; c <= c_last; ++c) nparts += (total * c / G != total * (c + 1) / G) ? 1 : 0;
@@ -794,12 +772,9 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         if (tid == 0) p.cnt[u] = 0;  // leave the counter clean for a caller that does not reset it
       }
     }
-    if (tid == 0) QWB_TL(30, 6 + 8 * segx);
-    ++segx;
     pre += nt_unit;
     ++u;
   }
-  if (tid == 0) QWB_TLB(1);
 }
 
 // Merge the partials of every unit that was cut across CTAs.  One block per unit, one warp per

@@ -10,13 +10,14 @@
 // exchange the per-tile instruction stream of the CUDA cores shrinks to the softmax of R rows, so
 // the kernel stays HBM-bound for 24-row verify batches where the mma.sync kernel is issue-bound.
 //
-// Layout and roles follow prefill_umma.cu: TMEM O | S0 | S1 (P over S), K/V through a ring of
+// Layout and roles follow prefill_umma2.cu: TMEM O | S0 | S1 (P over S), K/V through a ring of
 // eight 16 KB TMA slots released by tcgen05.commit, warp 0 = producer, warp 1 = MMA issuer and
 // TMEM owner, warps 2..17 = four softmax warpgroups (thread = row, warpgroup = 32-key column group
 // and 64-channel output group).  Differences: Q is staged by the softmax threads themselves (plain
 // loads, RoPE in double, bf16 hi + lo, written in the swizzled UMMA layout); each row has its own
 // causal limit; a CTA walks several segments (unit, tile range), so every barrier phase is tracked
 // with CTA-cumulative counters; a segment ends in a final store or in a partial + arrival ticket.
+#include <atomic>
 #include <cstring>
 
 #include "splitkv.cuh"
@@ -76,7 +77,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   DecCtl *ctl = reinterpret_cast<DecCtl *>(smem + DU_SMEM_TOTAL - sizeof(DecCtl));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) { QWB_TL(30, 0); QWB_TLB(0); }
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
   const int cta = blockIdx.x;
 
@@ -122,7 +122,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     if (warp == 1) tmem_dealloc(tmem, 512);
     return;
   }
-  if (tid == 0) QWB_TL(30, 2);
   // Advance (u, pre) to the next unit that has tiles inside this CTA's slice [g0, g1) of the flat
   // list; t0 / t1 bound those tiles.  The first LEAD entries of a unit stand for no tile.
   auto find_live = [&](int &u, long long &pre, int &nt, int &t0, int &t1) -> bool {
@@ -172,7 +171,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         const long long base = p.cache_row ? p.cache_row[ui.s] : 0;
         for (int j = t0; j <= t1 && ok; ++j) {
           if (j < t1) {
-            QWB_TL(10, j - t0);
             if (!dep_waited && (j + 1) * DU_BN > ui.pos) {  // first tile with rows of this step's append kernel
               grid_dep_wait();
               dep_waited = true;
@@ -188,7 +186,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
             }
           }
           if (j > t0 && ok) {
-            QWB_TL(11, j - 1 - t0);
             const int vrow = (int)cache_row_at(p.pages, base, ui.s, (j - 1) * DU_BN);
             for (int g = 0; g < 2 && ok; ++g) {
               if (!slot_ready()) break;
@@ -241,7 +238,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         if (j < t1) {
           // ---- S[Jt & 1] = Q K_j^T ----
           const uint32_t d_s = tmem + ((Jt & 1) ? TMEM_S1 : TMEM_S0);
-          QWB_TL(0, Jt); QWB_TL(31, Jt);
           for (int c2 = 0; c2 < 2 && ok; ++c2) {  // a slot = two 64-channel sub-tiles of the K tile
             if (!wait_all(&ctl->slot_full[sl], ph, DEV_ERR_MMA_WAIT)) break;
             tc_fence_after();
@@ -264,14 +260,12 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           }
         }
         if (j > t0 && ok) {
-          QWB_TL(1, Jt);
           // ---- O (+)= P_{j-1} V_{j-1} ----
           const int jj = j - 1, Jp = Jt - 1;
           if (!wait_all(&ctl->p_full[Jp & 1], (Jp >> 1) & 1, DEV_ERR_SOFTMAX_WAIT)) break;
           // the first P V of a segment overwrites O: the previous segment must have read it out
           if (jj == t0 && seg > 0 && !wait_all(&ctl->o_free, (seg - 1) & 1, DEV_ERR_SOFTMAX_WAIT)) break;
           tc_fence_after();
-          QWB_TL(2, Jp);
           const uint32_t a_p = tmem + ((Jp & 1) ? TMEM_S1 : TMEM_S0);
           for (int g = 0; g < 2 && ok; ++g) {  // a slot = 64 keys of the V tile
             if (!wait_all(&ctl->slot_full[sl], ph, DEV_ERR_MMA_WAIT)) break;
@@ -287,7 +281,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
             if (g == 1) umma_commit(&ctl->o_done[Jp & 1]);
             advance();
           }
-          QWB_TL(3, Jp);
         }
       }
       J += t1 - t0;
@@ -307,7 +300,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     int J = 0, o_seen = 0;
     bool ok = true;
     // P V completions are observed strictly in order (tile t: o_done[t & 1], phase t / 2)
-    int segx = 0;
     auto wait_pv_done = [&](int upto) {
       while (ok && o_seen <= upto) {
         ok = wait_or_abort(&ctl->o_done[o_seen & 1], (o_seen >> 1) & 1, abort_flag);
@@ -354,7 +346,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           float xr = 0.f, yr = 0.f;
           if (r < R) {
             const size_t trow = (size_t)ui.s * p.n_new + ui.tok0 + r / GROUP;
-            const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.pos + ui.tok0 + r / GROUP;
+            const int pz = p.mpos ? p.mpos[trow * 3 + mrope_component(i)] : ui.rpos + ui.tok0 + r / GROUP;
             float c, sn;
             rope_sincos_reduced(pz, p.rope.inv_freq[i], c, sn);
             const float x = bf16_bits_to_f32(rx[it]), y = bf16_bits_to_f32(ry[it]);
@@ -375,11 +367,9 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     // units cut across CTAs: their merge is settled after this CTA's last tile
     int pend_u[2] = {0, 0}, pend_nt[2] = {0, 0}, n_pend = 0;
     long long pend_pre[2] = {0, 0};
-    if (tid == 64) QWB_TL(30, 3);
     int nt, t0, t1;
     bool have = find_live(u, pre, nt, t0, t1);
     if (have) stage_q(unit_info(p, u));
-    if (tid == 64) QWB_TL(30, 4);
     while (have) {
       const UnitInfo ui = unit_info(p, u);
       // the unit this CTA works on next, if any: its Q tile is staged ahead of time (below)
@@ -397,9 +387,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       for (int j = t0; j < t1; ++j) {
         const int Jt = J + (j - t0);
         const uint32_t t_s = tmem + lane_sel + ((Jt & 1) ? TMEM_S1 : TMEM_S0);
-        if (tid == 64) QWB_TL(4, Jt);
         if (ok) ok = wait_or_abort(&ctl->s_full[Jt & 1], (Jt >> 1) & 1, abort_flag);
-        if (tid == 64) QWB_TL(5, Jt);
         tc_fence_after();
         uint32_t sr[32];
         float mx = -INFINITY;
@@ -420,10 +408,8 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
             for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
           }
         }
-        if (tid == 64) QWB_TL(6, Jt);
         ctl->mxbuf[Jt & 1][wg][row] = mx;
         asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
-        if (tid == 64) QWB_TL(7, Jt);
 #pragma unroll
         for (int w2 = 0; w2 < DU_NWG; ++w2) mx = fmaxf(mx, ctl->mxbuf[Jt & 1][w2][row]);
         const float m_new = fmaxf(m_used, mx * p.scale_log2);
@@ -490,16 +476,13 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         }
         tc_fence_before();
         mbar_arrive(&ctl->p_full[Jt & 1]);
-        if (tid == 64) QWB_TL(8, Jt);
         // Last tile of the segment: every Q K^T of this unit has completed (s_full above), so the Q
         // tile is free -- stage the next unit's rows while the tensor core runs this tile's P V.
         if (j == t1 - 1 && have_next) stage_q(unit_info(p, u_next));
         if (j > t0) wait_pv_done(Jt - 1);
-        if (tid == 64) QWB_TL(9, Jt);
       }
       // ---- end of the segment: read O out, release it, then store the result or a partial ----
       wait_pv_done(J + (t1 - t0) - 1);
-      if (tid == 64) QWB_TL(30, 5 + 6 * segx);
       ctl->lbuf[wg][row] = l_run;
       asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
       float l_tot = 0.f;
@@ -555,7 +538,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       // O has been read (or is abandoned): the next segment's first P V may overwrite it
       tc_fence_before();
       mbar_arrive(&ctl->o_free);
-      if (tid == 64) QWB_TL(30, 6 + 6 * segx);
       if (!all_ok) {
         if (lane == 0) fail(DEV_ERR_SOFTMAX_WAIT);
         break;
@@ -564,14 +546,11 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         pend_u[n_pend] = u; pend_nt[n_pend] = nt; pend_pre[n_pend] = pre;
         ++n_pend;
       }
-      if (tid == 64) QWB_TL(30, 7 + 6 * segx);
-      ++segx;
       J += t1 - t0;
       have = have_next;
       u = u_next; pre = pre_next; nt = nt_next; t0 = t0_next; t1 = t1_next;
     }
     // ---- units cut across CTAs are merged by whichever of their CTAs arrives last ----
-    if (tid == 64) QWB_TL(30, 50);
     if (n_pend > 0) {  // n_pend is the same in all softmax threads
       // which CTAs of c_first .. c_last hold a part (one thread per CTA: the test is two 64-bit divisions)
       for (int k = 0; k < n_pend; ++k) {
@@ -583,7 +562,6 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       // thread's (cumulative) fence and ticket; its second fence and the next barrier order the merge's loads
       // (which bypass L1) after the other CTAs' tickets
       asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
-      if (tid == 64) QWB_TL(30, 51);
       if (st_tid == 0) {  // one thread decides, so that a failure flagged meanwhile cannot split the group
         const int go = *abort_flag ? 0 : 1;
         __threadfence();
@@ -604,11 +582,8 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         ctl->merge_go = go;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
-      if (tid == 64) QWB_TL(30, 52);
       for (int k = 0; k < n_pend && ctl->merge_go; ++k) {
-        if (tid == 64) { QWB_TL(30, 53 + 3 * k); QWB_TLV(29, k, ctl->merge_parts[k] * 1000 + ctl->ticket[k]); }
         if (ctl->ticket[k] == ctl->merge_parts[k] - 1) {
-          if (tid == 64) QWB_TL(30, 54 + 3 * k);
           const int c_first = cta_of_tile(pend_pre[k] + LEAD, total, G), c_last = cta_of_tile(pend_pre[k] + LEAD + pend_nt[k] - 1, total, G);
           const UnitInfo ui = unit_info(p, pend_u[k]);
           const int R = ui.ntok * GROUP, span = c_last - c_first + 1;
@@ -616,17 +591,14 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
             merge_unit_row<TOut>(p, pend_u[k], ui, r, c_first, c_last, total, lane, G,
                                  span <= DU_MAX_PARTS ? ctl->merge_live[k] : nullptr);
           if (st_tid == 0) p.cnt[pend_u[k]] = 0;
-          if (tid == 64) QWB_TL(30, 55 + 3 * k);
         }
       }
     }
   }
 
   // ---- teardown ----
-  if (tid == 64) QWB_TL(30, 40);
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) QWB_TLB(1);
   if (warp == 1) {
     if (*abort_flag) {
       const uint64_t t0 = global_timer_ns();
@@ -652,14 +624,15 @@ void splitkv_umma_layout(int rb, int *q_rows_pad, int *nslot) {
 int launch_splitkv_umma(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, bool out_is_f32,
                         cudaStream_t st, bool dependent) {
   constexpr size_t smem = 1024 + DU_SMEM_TOTAL;
-  static bool configured[64] = {false};
+  // once per device; the step is idempotent, so an atomic flag is all that concurrent host threads need
+  static std::atomic<int> configured[64];
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  if (dev < 0 || !configured[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(splitkv_umma_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
         cudaFuncSetAttribute(splitkv_umma_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return 3;
-    configured[dev] = true;
+    if (dev >= 0) configured[dev].store(1, std::memory_order_release);
   }
   if (out_is_f32)
     launch_kernel(splitkv_umma_kernel<float>, dim3(p.G), dim3(DU_THREADS), smem, st, dependent, mk, mv, p);

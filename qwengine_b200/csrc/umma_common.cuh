@@ -10,10 +10,6 @@ namespace qwb {
 constexpr float PF_RESCALE_THRESHOLD = 8.f;  // log2 units: rescale O only when the max grows by > 2^8
 constexpr uint32_t TMEM_O = 0, TMEM_S0 = 256, TMEM_S1 = 384;
 
-// Timeline probe for kernel bring-up: with -DQWB_TIMELINE one CTA records clock64() at named
-// events into a caller-supplied buffer [event][tile]; compiled out otherwise.
-
-
 struct PrefillParams {
   const uint16_t *gate;
   void *out;
@@ -21,6 +17,7 @@ struct PrefillParams {
   const int64_t *cache_row;
   PageMap pages;
   const int *pos;
+  const int *q_pos;  // null, or the absolute position of each sequence's first new row (RoPE angles)
   const int *mpos;
   int *status;
   int n_seq, n_new, q_heads, kv_heads, n_qtiles;
@@ -28,8 +25,6 @@ struct PrefillParams {
   int do_rope, out_is_f32;
   int fast_p;       // 1: single bf16 P (no lo pass)
   RopeTable rope;
-  unsigned long long *dbg;  // timeline probe (only written when built with QWB_TIMELINE)
-  int dbg_block;
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------------------

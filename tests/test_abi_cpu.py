@@ -33,7 +33,7 @@ def test_library_builds_and_exports_every_declared_symbol():
 
 def test_host_only_entry_points():
     l = api.lib()
-    assert l.qw_abi_version() == 2
+    assert l.qw_abi_version() == 3
     assert l.qw_strerror(0) == b"ok" and b"geometry" in l.qw_strerror(2)
     assert l.qw_attn_decode_scratch_floats(24, 4, 8192, 1) <= 1 * 24 * 8192
     assert l.qw_attn_decode_scratch_floats(24, 4, 512, 8) <= 8 * 24 * 512

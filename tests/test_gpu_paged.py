@@ -80,13 +80,6 @@ def test_paged_cache_equals_contiguous(name, page_rows):
             assert np.array_equal(vc_p[row], vc_o[int(c.cache_row[s]) + t])
 
 
-def test_paged_cache_one_cta_prefill_kernel():
-    c = Case(206, [200], 128, kv_heads=1)
-    out_c, _, _, _, _ = run_case(c, out_f32=True, flags=api.F_ROPE | api.F_APPEND | api.F_GATE | api.F_UMMA_1CTA)
-    out_p, _, _, _, _ = _run_paged(c, 128, 7, flags=api.F_ROPE | api.F_APPEND | api.F_GATE | api.F_UMMA_1CTA)
-    assert np.array_equal(out_p, out_c)
-
-
 def test_paged_cache_argument_errors():
     c = Case(207, [10], 1)
     mx = api.Mixer(1, 1)

@@ -147,43 +147,39 @@ def test_prefill_chunk_splitkv(hist, T):
 
 # ---- prefill on the tcgen05 kernels (chunks of >= 64 rows) ------------------------------------------------
 _FUSED = api.F_ROPE | api.F_APPEND | api.F_GATE
-_KERNELS = {"pair": 0, "single": api.F_UMMA_1CTA}
 
 
-@pytest.mark.parametrize("kernel", sorted(_KERNELS))
 @pytest.mark.parametrize("hist,T,kvh", [([0], 128, 1), ([0], 64, 2), ([0], 256, 1), ([100], 200, 2), ([37], 333, 1),
                                         ([500, 3], 96, 1), ([0], 512, 4), ([1000], 128, 4), ([3000], 640, 1)])
-def test_prefill_umma(kernel, hist, T, kvh):
+def test_prefill_umma(hist, T, kvh):
     c = Case(55 + T, hist, T, kv_heads=kvh)
     ref, lse_ref, kc_ref, vc_ref = c.oracle()
-    o32, lse, kc, vc, mx = run_case(c, out_f32=True, flags=_FUSED | _KERNELS[kernel])
+    o32, lse, kc, vc, mx = run_case(c, out_f32=True, flags=_FUSED)
     assert mx.launches() == 2, "expected rope_append + the tcgen05 kernel"
     assert np.array_equal(kc, kc_ref) and np.array_equal(vc, vc_ref)
     check_out(o32, ref, "prefill umma")
     check_lse(lse, lse_ref, "prefill umma")
-    o16, _, _, _, _ = run_case(c, out_f32=False, flags=_FUSED | _KERNELS[kernel])
+    o16, _, _, _, _ = run_case(c, out_f32=False, flags=_FUSED)
     check_out_bf16(o16, ref, "prefill umma bf16")
     assert np.array_equal(O.f32_to_bf16_bits(o32), O.f32_to_bf16_bits(o16))
 
 
-@pytest.mark.parametrize("kernel", sorted(_KERNELS))
-def test_prefill_umma_fast_p_mode(kernel):
+def test_prefill_umma_fast_p_mode():
     """QW_F_FAST_P drops the bf16 lo pass of P: still inside max-abs, rel-L2 up to ~2e-3 by design."""
     c = Case(57, [700], 384, kv_heads=1)
     ref, lse_ref, _, _ = c.oracle()
-    o32, lse, _, _, _ = run_case(c, out_f32=True, flags=_FUSED | api.F_FAST_P | _KERNELS[kernel])
+    o32, lse, _, _, _ = run_case(c, out_f32=True, flags=_FUSED | api.F_FAST_P)
     assert np.abs(o32 - ref).max() <= 2e-2 and 5e-4 < rel_l2(o32, ref) <= 2.5e-3
     check_lse(lse, lse_ref, "fast p")
 
 
-@pytest.mark.parametrize("kernel", sorted(_KERNELS))
-def test_prefill_umma_mrope_and_stale_rows(kernel):
+def test_prefill_umma_mrope_and_stale_rows():
     """mrope positions, a ragged last tile, and NaN bit patterns in the cache rows past the end."""
     c = Case(58, [70], 130, kv_heads=1, mrope=True, pad_rows=200)
     c.kc0[c.kc0 == 0x4F00] = 0x7FC0
     c.vc0[c.vc0 == 0x4F00] = 0x7FC0
     ref, lse_ref, kc_ref, _ = c.oracle()
-    o32, lse, kc, _, _ = run_case(c, out_f32=True, flags=_FUSED | _KERNELS[kernel])
+    o32, lse, kc, _, _ = run_case(c, out_f32=True, flags=_FUSED)
     n = (70 + 130) * 256
     assert np.array_equal(kc.reshape(-1)[:n], kc_ref.reshape(-1)[:n])
     assert np.isfinite(o32).all()
@@ -191,11 +187,10 @@ def test_prefill_umma_mrope_and_stale_rows(kernel):
     check_lse(lse, lse_ref, "prefill umma mrope")
 
 
-@pytest.mark.parametrize("kernel", sorted(_KERNELS))
-def test_prefill_umma_bitwise_repeatable(kernel):
+def test_prefill_umma_bitwise_repeatable():
     c = Case(56, [260], 512, kv_heads=2)
-    a = run_case(c, flags=_FUSED | _KERNELS[kernel])
-    b = run_case(c, flags=_FUSED | _KERNELS[kernel])
+    a = run_case(c, flags=_FUSED)
+    b = run_case(c, flags=_FUSED)
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
 
 
