@@ -69,3 +69,26 @@ def test_header_is_plain_c_and_cpp_mirror_compiles():
         root, "qwengine_b200", "csrc", "mixer.hpp")
     subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-I", os.path.join(root, "include"), "-I", cuda_inc, "-x", "c++", "-"],
                    input=src.encode(), check=True)
+
+
+def test_workspace_errors_come_before_any_launch():
+    """A call that returns QW_ERR_WORKSPACE has enqueued nothing: the workspace is checked in front of the append
+    kernel, so a caller may fix the workspace and repeat the call without appending its rows twice.  Needs no GPU:
+    the call returns before it touches the CUDA runtime."""
+    l = api.lib()
+    buf = (ctypes.c_float * 64)()
+    p = ctypes.cast(buf, ctypes.c_void_p).value
+    d = api.MixerDesc()
+    d.n_seq, d.n_new, d.q_heads, d.kv_heads, d.head_dim, d.rotary_dim = 2, 4, 24, 4, 256, 64
+    d.theta, d.scale, d.flags = 1e7, 0.0625, api.F_ROPE | api.F_APPEND | api.F_GATE
+    d.q = d.k_new = d.v_new = d.gate = d.out = d.kc = d.vc = d.pos = p
+    d.cache_rows = 1024
+    need = l.qw_mixer_workspace_bytes(ctypes.byref(d))
+    assert need > 4096
+    for ws, nbytes in ((None, need), (p, 64), (p, 4096), (p + 4, need)):   # missing, tiny, one slot short, misaligned
+        d.workspace, d.workspace_bytes = ws, nbytes
+        assert l.qw_mixer_forward(ctypes.byref(d), None) == 4
+        assert l.qw_last_launch_count() == 0
+    # the same holds for the drop-in decode launcher when ctx is too small for one partial
+    assert l.qw_attn_decode_bf16(p, p, p, p, p, 256, 4, 24, 0.0625, p, 16, 1, None) == 4
+    assert l.qw_last_launch_count() == 0

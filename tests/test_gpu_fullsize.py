@@ -112,3 +112,42 @@ def test_maximum_context_decode():
     assert np.array_equal(kc[n], kc_ref[n])
     check_out(out, ref, "max context")
     check_lse(lse, lse_ref, "max context")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_dropin_prefill_last_chunk_of_a_32k_prompt(dtype):
+    """The reference's own prefill launch site (src/prefill.cu:142-154) at its hardest shape: a 2048-token chunk
+    behind 30720 cached tokens, all four KV heads, through qw_rope / qw_kv_append / qw_attn_prefill.  It must run
+    on the tcgen05 kernel, agree with the oracle on sampled rows, and agree with the fused call on everything."""
+    T, pos0, ctx = 2048, 30720, 32768
+    c = Case(310, [pos0], T)
+    q = torch.from_numpy(c.q[0]).cuda().to(dtype)
+    k = torch.from_numpy(c.k[0]).cuda().to(dtype)
+    v = torch.from_numpy(c.v[0]).cuda().to(dtype)
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    scratch = torch.empty(api.attn_prefill_scratch_floats(24, 4, ctx, T), dtype=torch.float32, device="cuda")
+    api.rope(q, 24, 256, 64, dpos, 1e7, B=T)
+    api.rope(k, 4, 256, 64, dpos, 1e7, B=T)
+    api.kv_append(k, v, kc, vc, dpos, 1024, B=T)
+    api.attn_prefill(q, kc, vc, out, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, T)
+    torch.cuda.synchronize()
+    assert api.last_attention_kernel() == "prefill_umma_pair_kernel"
+    got = host_f32(out)
+    assert np.isfinite(got).all()
+    rows = [0, 127, 128, 1000, 2047]
+    ref, _, kc_ref, vc_ref = c.oracle(rows=rows, do_gate=False)
+    assert np.array_equal(host_bits(kc), kc_ref) and np.array_equal(host_bits(vc), vc_ref)
+    # attention alone, on the q the tensor cores read
+    q_seen = host_f32(q.to(torch.bfloat16))[None]
+    ref_attn, _ = O.mixer(q_seen, None, None, None, kc_ref.copy(), vc_ref.copy(), [pos0], rows=rows, do_rope=False,
+                          do_append=False, do_gate=False)
+    assert np.abs(got[rows] - ref_attn).max() <= 2e-2 and rel_l2(got[rows], ref_attn) <= (1e-3 if dtype == torch.float32 else 2e-3)
+    assert np.abs(got[rows] - ref).max() <= 2e-2 and rel_l2(got[rows], ref) <= (2e-3 if dtype == torch.float32 else 4e-3)
+    # the fused call (q rotated inside, in fp32) on the same inputs, gate off
+    import copy
+    cg = copy.copy(c)
+    cg.gate = None
+    fused, _, _, _, _ = run_case(cg, out_f32=True)
+    assert np.abs(got - fused).max() <= 2e-2 and rel_l2(got, fused) <= (2e-3 if dtype == torch.float32 else 4e-3)

@@ -252,6 +252,66 @@ def test_dropin_sequence_like_model_cu(dtype, B):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B", [1, 4, 8])
+def test_dropin_decode_uses_no_more_scratch_than_documented(dtype, B):
+    """The decode launcher may use B * q_heads * ctx floats of scratch (what the reference's kernel needs at the
+    same launch) and not one more: sentinel words behind that size stay untouched."""
+    ctx, pos0 = 1024, 900
+    c = Case(65 + B, [pos0], B, pad_rows=ctx - pos0 - B)
+    _, _, kc_ref, vc_ref = c.oracle()
+    q = torch.from_numpy(c.q[0]).cuda().to(dtype)
+    kc, vc = dev_bits(kc_ref), dev_bits(vc_ref)
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    out = torch.empty_like(q)
+    n = api.attn_decode_scratch_floats(24, 4, ctx, B)
+    assert n == B * 24 * ctx
+    guard = 1 << 20
+    scratch = torch.full((n + guard,), -7.25, dtype=torch.float32, device="cuda")
+    api.attn_decode(q, kc, vc, out, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, B=B)
+    torch.cuda.synchronize()
+    assert bool((scratch[n:] == -7.25).all()), "the launcher wrote past the documented scratch size"
+    assert bool(torch.isfinite(out.float()).all())
+    want = "splitkv_umma_kernel" if (dtype == torch.bfloat16 and B >= 2) else "splitkv_kernel"
+    assert api.last_attention_kernel() == want
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("pos0,T,ctx", [(0, 64, 256), (300, 256, 1024), (1000, 333, 2048)])
+def test_dropin_prefill_reaches_the_tcgen05_kernel(dtype, pos0, T, ctx):
+    """qw_attn_prefill_* with a chunk of 64 rows or more, as src/prefill.cu:142-154 would call it: rope, append,
+    attention (no gate).  The attention is compared with the oracle fed with the very q the kernel got (tight), and
+    the whole sequence with the oracle's own fp32 pipeline (the bf16 roundings of this route on top)."""
+    c = Case(170 + T, [pos0], T, pad_rows=ctx - pos0 - T)
+    ref, _, kc_ref, vc_ref = c.oracle(do_gate=False)
+    q = torch.from_numpy(c.q[0]).cuda().to(dtype)
+    k = torch.from_numpy(c.k[0]).cuda().to(dtype)
+    v = torch.from_numpy(c.v[0]).cuda().to(dtype)
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    scratch = torch.empty(api.attn_prefill_scratch_floats(24, 4, ctx, T), dtype=torch.float32, device="cuda")
+    api.rope(q, 24, 256, 64, dpos, 1e7, B=T)
+    api.rope(k, 4, 256, 64, dpos, 1e7, B=T)
+    api.kv_append(k, v, kc, vc, dpos, 1024, B=T)
+    api.attn_prefill(q, kc, vc, out, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, T)
+    torch.cuda.synchronize()
+    assert api.last_attention_kernel() == "prefill_umma_pair_kernel"
+    assert np.array_equal(host_bits(kc), kc_ref) and np.array_equal(host_bits(vc), vc_ref)
+    got = host_f32(out)
+    # (1) attention alone: the oracle on the rotated q as the tensor cores read it (bf16), same cache
+    q_seen = host_f32(q.to(torch.bfloat16))[None]
+    kcn, vcn = kc_ref.copy(), vc_ref.copy()
+    ref_attn, _ = O.mixer(q_seen, None, None, None, kcn, vcn, [pos0], do_rope=False, do_append=False, do_gate=False)
+    if dtype == torch.float32:
+        check_out(got, ref_attn, "drop-in prefill f32, attention alone")
+        # (2) end to end against the fp32 pipeline: q was rounded to bf16 on its way to the tensor cores
+        assert np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 2e-3
+    else:
+        check_out_bf16(got, ref_attn, "drop-in prefill bf16, attention alone")
+        assert np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 4e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_dropin_prefill_like_prefill_cu(dtype):
     ctx, pos0, T = 512, 100, 50
     c = Case(70, [pos0], T, pad_rows=ctx - pos0 - T)
@@ -367,3 +427,34 @@ def test_short_chunks_all_tile_layouts(n_new):
     """Chunk lengths around the row-tile limits of the tcgen05 split-KV kernel: 10 / 11 tokens (60 / 66 rows: the
     64- and 128-row Q tiles), 21 (126 rows, one block) and 22, 63 (two and three blocks per sequence and KV head)."""
     _full_check(Case(120 + n_new, [513, 64, 1290], n_new, kv_heads=2), "chunk of %d" % n_new)
+
+
+# ---- a launch that finds the status word already set leaves at once --------------------------------------
+@pytest.mark.parametrize("hist,n_new", [([900, 70], 4), ([300], 256)])
+def test_launch_with_status_word_already_set_does_nothing(hist, n_new):
+    """After a kernel has reported a failure through the status word, later launches that share the word must not
+    keep the GPU busy with further waits: the tcgen05 kernels read it first and leave (no output, no hang)."""
+    c = Case(180 + n_new, hist, n_new)
+    mx = api.Mixer(c.n_seq, n_new)
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    out = torch.full((c.n_seq, n_new, 24, 256), 3.0, dtype=torch.float32, device="cuda")
+    mx.bind(dev_bf16(c.q), kc, vc, torch.from_numpy(c.hist).cuda(), out, k_new=dev_bf16(c.k), v_new=dev_bf16(c.v),
+            gate=dev_bf16(c.gate), cache_row=torch.from_numpy(c.cache_row).cuda())
+    mx.status.fill_(103)
+    mx.forward()
+    torch.cuda.synchronize()
+    assert api.last_attention_kernel() in ("splitkv_umma_kernel", "prefill_umma_pair_kernel")
+    assert int(mx.status.item()) == 103
+    assert bool((out == 3.0).all()), "a launch that found the status word set still wrote output"
+    with pytest.raises(api.QwError):
+        mx.check_status()
+    # cleared, the same call goes through
+    mx.status.zero_()
+    kc2, vc2 = dev_bits(c.kc0), dev_bits(c.vc0)
+    mx.bind(dev_bf16(c.q), kc2, vc2, torch.from_numpy(c.hist).cuda(), out, k_new=dev_bf16(c.k), v_new=dev_bf16(c.v),
+            gate=dev_bf16(c.gate), cache_row=torch.from_numpy(c.cache_row).cuda())
+    mx.forward()
+    torch.cuda.synchronize()
+    mx.check_status()
+    ref, _, _, _ = c.oracle()
+    check_out(host_f32(out).reshape(-1, 24, 256), ref, "after clearing the status word")
