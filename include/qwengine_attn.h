@@ -155,9 +155,14 @@ enum {
   QW_F_NO_UMMA = 16,   /* force the split-KV kernel even for long prefill chunks        */
   QW_F_FAST_P = 32,    /* tcgen05 prefill only: feed P as one bf16 instead of a bf16 hi+lo
                           pair; 1/3 less tensor work, output rel-L2 ~1.4e-3 instead of 2e-6 */
-  QW_F_NO_CAUSAL = 128 /* every row sees exactly pos[s] (>= 1) keys of its sequence: the call covers
+  QW_F_NO_CAUSAL = 128, /* every row sees exactly pos[s] (>= 1) keys of its sequence: the call covers
                           a KV sub-range that does not contain the new rows (cross-GPU KV split);
                           excludes QW_F_APPEND; with QW_F_ROPE the descriptor must carry q_pos    */
+  QW_F_NO_ATTENTION = 256 /* with QW_F_APPEND: rotate k_new and store k_new / v_new, nothing else (q, gate, out
+                          and workspace are not touched and may be NULL).  For a rank that holds a whole
+                          chunk's keys but computes only some of its query rows (query-row split of one
+                          sequence over a GPU pair): it appends the chunk once, then attends per row block
+                          without QW_F_APPEND                                                        */
 };
 
 typedef struct qw_mixer_desc {

@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libqwengine_attn.so")
 
 QW_OK = 0
-F_ROPE, F_APPEND, F_GATE, F_OUT_F32, F_NO_UMMA, F_FAST_P, F_NO_CAUSAL = 1, 2, 4, 8, 16, 32, 128
+F_ROPE, F_APPEND, F_GATE, F_OUT_F32, F_NO_UMMA, F_FAST_P, F_NO_CAUSAL, F_NO_ATTENTION = 1, 2, 4, 8, 16, 32, 128, 256
 PARTIAL_FLOATS = 260
 HEAD_DIM, ROTARY_DIM, GROUP = 256, 64, 6
 
@@ -167,6 +167,22 @@ class Mixer:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         d.workspace, d.workspace_bytes, d.status = self.workspace.data_ptr(), nbytes, self.status.data_ptr()
         self._keep = None
+
+    def bind_append_only(self, kc, vc, pos, k_new, v_new, cache_row=None, mpos=None, block_table=None, page_rows=0,
+                         q_pos=None, rope=True):
+        """Descriptor for QW_F_NO_ATTENTION: forward() then only rotates k_new and stores k_new / v_new."""
+        d = self.desc
+        d.flags = F_APPEND | F_NO_ATTENTION | (F_ROPE if rope else 0)
+        d.q = d.gate = d.out = d.lse = None
+        d.k_new, d.v_new, d.kc, d.vc = k_new.data_ptr(), v_new.data_ptr(), kc.data_ptr(), vc.data_ptr()
+        d.cache_rows = kc.numel() // (self.kv_heads * HEAD_DIM)
+        d.cache_row, d.pos, d.mpos = _addr(cache_row), pos.data_ptr(), _addr(mpos)
+        d.block_table = _addr(block_table)
+        d.block_table_stride = 0 if block_table is None else int(block_table.shape[-1])
+        d.page_rows = int(page_rows)
+        d.q_pos = _addr(q_pos)
+        self._keep = (kc, vc, pos, k_new, v_new, cache_row, mpos, block_table, q_pos)
+        return self
 
     def bind(self, q, kc, vc, pos, out, k_new=None, v_new=None, gate=None, lse=None, cache_row=None,
              mpos=None, flags=F_ROPE | F_APPEND | F_GATE, fused=False, block_table=None, page_rows=0, q_pos=None):

@@ -341,7 +341,9 @@ struct FusedRows {
 
 bool desc_ok(const qw_mixer_desc *d, const FusedRows *fr) {
   if (!d || d->n_seq < 0 || d->n_new < 0) return false;
-  if (!d->q || !d->out || !d->kc || !d->vc || !d->pos || d->cache_rows <= 0) return false;
+  if (!d->kc || !d->vc || !d->pos || d->cache_rows <= 0) return false;
+  if (d->flags & QW_F_NO_ATTENTION) return !fr && (d->flags & QW_F_APPEND) && d->k_new && d->v_new;
+  if (!d->q || !d->out) return false;
   if (fr) {
     if (!fr->rows || !fr->q_norm_w || !fr->k_norm_w || !d->gate || !(d->flags & QW_F_APPEND)) return false;
   } else if ((d->flags & QW_F_APPEND) && (!d->k_new || !d->v_new)) {
@@ -397,6 +399,13 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
   if ((d->flags & QW_F_NO_CAUSAL) && (d->flags & QW_F_APPEND)) return QW_ERR_ARG;  // a sub-range call never owns the new rows
   // the rows of a sub-range call do not sit at pos[s] + b: their angles need q_pos (or mpos)
   if ((d->flags & QW_F_NO_CAUSAL) && (d->flags & QW_F_ROPE) && !d->q_pos && !d->mpos) return QW_ERR_ARG;
+  if (d->flags & QW_F_NO_ATTENTION) {  // rope(k) + append only
+    if (partial) return QW_ERR_ARG;
+    rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
+        d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
+        (d->flags & QW_F_ROPE) ? 1 : 0, tab, nullptr, 0, pm, d->q_pos);
+    return check_launch("rope_append_kernel");
+  }
   const bool use_umma =
       !(d->flags & (QW_F_NO_UMMA | QW_F_NO_CAUSAL)) && !partial && prefill_umma_supported(d->n_new);
   // Workspace of the split-KV kernels: arrival counters (one per unit), then the partial slots.  The
