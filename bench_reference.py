@@ -54,9 +54,17 @@ def _reference_gpu(args, w):
     scratch = torch.empty(n_new * 24 * max_ctx, dtype=torch.float32, device="cuda")
     st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
-    def step():
+    prefill_like = prefill
+    steps = max(1, min(args.steps, 3 if prefill_like else 20))
+    warm = max(1, min(args.warmup, 1 if prefill_like else 5))
+    # rope works in place: every step needs its own un-rotated copy of q and k, made outside the timed region
+    for s in seqs:
+        s["qs"] = [s["q0"].clone() for _ in range(steps + warm)]
+        s["ks"] = [s["k0"].clone() for _ in range(steps + warm)]
+
+    def step(i):
         for s in seqs:
-            q, k = s["q0"].clone(), s["k0"].clone()   # rope works in place; start from un-rotated rows
+            q, k = s["qs"][i], s["ks"][i]
             l.ref_rope(p(q), 24, 256, 64, p(s["dpos"]), 1e7, st, n_new, None)
             l.ref_rope(p(k), 4, 256, 64, p(s["dpos"]), 1e7, st, n_new, None)
             l.ref_kv_append(p(k), p(s["v"]), p(s["kc"]), p(s["vc"]), p(s["dpos"]), 1024, n_new, st)
@@ -68,15 +76,13 @@ def _reference_gpu(args, w):
                                   p(scratch), s["ctx"], n_new, st)
             l.ref_gate_sigmoid(p(s["out"]), p(s["gate"]), n_new * 6144, st)
 
-    steps = max(1, min(args.steps, 3 if prefill else 20))
-    warm = 1 if prefill else 3
-    for _ in range(warm):
-        step()
+    for i in range(warm):
+        step(i)
     torch.cuda.synchronize()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     ev[0].record()
-    for _ in range(steps):
-        step()
+    for i in range(steps):
+        step(warm + i)
     ev[1].record()
     torch.cuda.synchronize()
     return ev[0].elapsed_time(ev[1]) / steps, steps, warm
@@ -120,7 +126,7 @@ def run_reference(args, rank, local_rank, world):
         "scaling": "weak", "vs_baseline": None, "dtype": "f32" if kind == "reference" else "f64",
         "data": "synthetic: the same seeded tensors as the B200 arm, widened to fp32",
         "config": {"workload": bench.describe(name, 1, w), "how": how,
-                   "ranks": "rank 0 alone runs one GPU's share of the weak-scaled batch; the value is per GPU",
+                   "ranks": "rank 0 alone runs one GPU's share of the weak-scaled batch: the reference serves one sequence on one GPU (README.md:365-367), so its rate does not grow with N",
                    "note": "algorithmic unit is the same as the B200 arm's (4096 B of bf16 K+V per cached token, "
                            "24576 FLOP per pair); the reference itself moves fp32"},
         "cpu_baseline": dict(cpu, kind="port") if cpu else {"kind": kind, "cores": cores, "sample": how, "value": round(value, 4) if value else None, "unit": unit},

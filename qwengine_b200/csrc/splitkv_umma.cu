@@ -36,7 +36,9 @@ constexpr int DU_NWG = 4;
 constexpr int DU_MAX_PARTS = 256;         // CTAs of one unit whose liveness is tabulated for the merge
 constexpr int DU_SWITCH_TILES = 4;        // least number of tiles of time a CTA loses where its slice crosses into the next unit
 constexpr int DU_SM_THREADS = DU_NWG * 128;
-constexpr int DU_THREADS = 64 + DU_SM_THREADS;
+constexpr int DU_CTL_THREADS = 128;        // control warpgroup: TMA producer, MMA issuer, the partition warp, one idle warp
+constexpr int DU_THREADS = DU_CTL_THREADS + DU_SM_THREADS;
+constexpr int DU_CTL_REGS = 64, DU_SM_REGS = 104;  // after setmaxnreg: 128 x 64 + 512 x 104 = the 640 x 96 registers the block starts with
 
 struct DecCtl {
   uint64_t q_ready, o_free, s_full[2], p_full[2], o_done[2];
@@ -142,7 +144,12 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     *abort_flag = 1;
   };
 
+  // Registers: five warpgroups start with 96 per thread; the control warpgroup hands a third of its share to
+  // the four softmax warpgroups (setmaxnreg, first thing in each branch: the compiler changes the register
+  // budget only for code that the instruction dominates), so the softmax loop holds its 64 values of S and P
+  // per thread without spilling.
   if (warp == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DU_CTL_REGS));
     // =============================== TMA producer ===========================================
     // Per segment the slot stream is  K_t0 | K_t0+1 V_t0 | ... | V_t1-1 ; segments follow each
     // other without a gap.  A K slot is two 64-channel sub-tiles of 128 keys, a V slot 64 keys x 256 channels
@@ -202,6 +209,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       }
     }
   } else if (warp == 1) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DU_CTL_REGS));
     // =============================== MMA issuer ==============================================
     // One elected thread walks the tile sequence and issues everything.  J counts tiles over all segments of this CTA: S / P buffer J & 1,
     // barrier phase J >> 1.
@@ -289,11 +297,14 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       ++u;
     }
     }
+  } else if (warp < DU_CTL_THREADS / 32) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DU_CTL_REGS));  // the other two warps of the control warpgroup
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DU_SM_REGS));
     // ============ softmax / correction / epilogue: thread = (row, 32-key column group) ============
-    const int wg = (warp - 2) >> 2;
+    const int wg = (warp - DU_CTL_THREADS / 32) >> 2;
     const int row = (warp & 3) * 32 + lane;
-    const int st_tid = tid - 64;                          // 0 .. 511
+    const int st_tid = tid - DU_CTL_THREADS;              // 0 .. 511
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     int u = (int)ctl->part[2];
     long long pre = ctl->part[1];
@@ -438,19 +449,22 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         if (warp_live) {
           const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
           float lsum = 0.f;
-          uint32_t hi[16], lo[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[i]), p.scale_log2, -m_sub));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), p.scale_log2, -m_sub));
-            lsum += p0 + p1;
-            const uint32_t h = pack_bf16(p0, p1);
-            hi[i >> 1] = h;
-            lo[i >> 1] = pack_bf16(p0 - bf16lo(h), p1 - bf16hi(h));
+          for (int h2 = 0; h2 < 2; ++h2) {  // 16 keys at a time: fewer packed values live at once
+            uint32_t hi[8], lo[8];
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[h2 * 16 + i]), p.scale_log2, -m_sub));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[h2 * 16 + i + 1]), p.scale_log2, -m_sub));
+              lsum += p0 + p1;
+              const uint32_t h = pack_bf16(p0, p1);
+              hi[i >> 1] = h;
+              lo[i >> 1] = pack_bf16(p0 - bf16lo(h), p1 - bf16hi(h));
+            }
+            tmem_st8(t_s + wg * 16 + h2 * 8, hi);
+            tmem_st8(t_s + 64 + wg * 16 + h2 * 8, lo);
           }
           l_run += lsum;
-          tmem_st16(t_s + wg * 16, hi);
-          tmem_st16(t_s + 64 + wg * 16, lo);
           tmem_wait_st();
         }
         // Keys past the end of the unit may hold anything in V; P is zero there but 0 * NaN is NaN,
@@ -587,7 +601,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           const int c_first = cta_of_tile(pend_pre[k] + LEAD, total, G), c_last = cta_of_tile(pend_pre[k] + LEAD + pend_nt[k] - 1, total, G);
           const UnitInfo ui = unit_info(p, pend_u[k]);
           const int R = ui.ntok * GROUP, span = c_last - c_first + 1;
-          for (int r = warp - 2; r < R; r += DU_NWG * 4)
+          for (int r = warp - DU_CTL_THREADS / 32; r < R; r += DU_NWG * 4)
             merge_unit_row<TOut>(p, pend_u[k], ui, r, c_first, c_last, total, lane, G,
                                  span <= DU_MAX_PARTS ? ctl->merge_live[k] : nullptr);
           if (st_tid == 0) p.cnt[pend_u[k]] = 0;

@@ -56,6 +56,41 @@ def partition_by_kv_bytes(kv_lens, n_bins, max_share=None):
     return bins
 
 
+def partition_for_exchange(kv_lens, n_bins, align=128, max_piece=None):
+    """Partition for a step whose split sequences are merged by one exchange of per-rank partials: greedy
+    longest-first by KV bytes like partition_by_kv_bytes, but a sequence longer than the per-bin share
+    (total / n_bins) is cut into ceil(len / share) nearly equal ranges (cuts on multiples of `align`, so that no
+    K/V tile or cache page straddles a cut) which go to DISTINCT bins -- every rank then holds at most one
+    range of a sequence and contributes one partial row per split sequence.  `max_piece` lowers the length
+    above which a sequence is cut (a serving step bounds the latency of its longest sequence that way).
+    Returns n_bins lists of (seq, start, end); every token of every sequence appears exactly once."""
+    lens = [int(x) for x in kv_lens]
+    total = sum(lens)
+    share = max(align, -(-total // n_bins))
+    if max_piece is not None:
+        share = max(align, min(share, int(max_piece)))
+    bins, load = [[] for _ in range(n_bins)], [0] * n_bins
+    for s in sorted(range(len(lens)), key=lambda i: (-lens[i], i)):
+        L = lens[s]
+        n_cut = min(n_bins, -(-L // share)) if (L > share and n_bins > 1) else 1
+        if n_cut <= 1:
+            b = min(range(n_bins), key=lambda i: (load[i], i))
+            bins[b].append((s, 0, L))
+            load[b] += L
+            continue
+        step = -(-(-(-L // n_cut)) // align) * align          # ceil(L / n_cut) rounded up to the alignment
+        cuts = [min(L, i * step) for i in range(n_cut + 1)]
+        cuts[-1] = L
+        pieces = [(cuts[i], cuts[i + 1]) for i in range(n_cut) if cuts[i + 1] > cuts[i]]
+        targets = sorted(range(n_bins), key=lambda i: (load[i], i))[:len(pieces)]
+        for b, (a, e) in zip(targets, sorted(pieces, key=lambda r: -(r[1] - r[0]))):
+            bins[b].append((s, a, e))
+            load[b] += e - a
+    for b in bins:
+        b.sort()
+    return bins
+
+
 def gather_partials(partial, group=None):
     """All-gathers one rank's partials [rows, q_heads, 260] into [world, rows, q_heads, 260],
     ordered by rank, which is also the order the merge uses (fixed => bit-stable)."""

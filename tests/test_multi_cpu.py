@@ -28,6 +28,33 @@ def test_shard_plans_cover_all_heads_and_sequences():
         sharding.shard_plan(3, 0)
 
 
+def test_partition_for_exchange_gives_every_rank_at_most_one_range_of_a_sequence():
+    """The partition behind the one-exchange merge: exact cover, cuts on tile boundaries, a cut sequence's ranges on
+    distinct ranks, balanced loads; and the query-row split of a chunk over a GPU pair has equal causal work."""
+    rng = np.random.default_rng(6)
+    lens = np.exp(rng.uniform(np.log(512), np.log(131072), 64)).astype(int) + 1
+    for world in (1, 2, 4, 8):
+        bins = sharding.partition_for_exchange(lens, world, max_piece=32768)
+        assert len(bins) == world
+        per_seq = {}
+        for r, b in enumerate(bins):
+            for s, a, e in b:
+                assert 0 <= a < e <= lens[s] and (a % 128 == 0)
+                per_seq.setdefault(s, []).append((a, e, r))
+        for s, L in enumerate(lens):
+            rs = sorted(per_seq[s])
+            assert rs[0][0] == 0 and rs[-1][1] == L and all(rs[i][1] == rs[i + 1][0] for i in range(len(rs) - 1))
+            assert len({r for _, _, r in rs}) == len(rs), "two ranges of one sequence on one rank"
+            if world == 1:
+                assert len(rs) == 1
+        load = [sum(e - a for _, a, e in b) for b in bins]
+        assert max(load) <= 1.02 * sum(load) / world
+    # zig-zag query-row split of a 2048-row chunk behind h cached tokens: rows [0,512) + [1536,2048) vs [512,1536)
+    pairs = lambda h, off, n: n * (h + off) + n * (n + 1) // 2
+    for h in (0, 2048, 30720):
+        assert pairs(h, 0, 512) + pairs(h, 1536, 512) == pairs(h, 512, 1024)
+
+
 def test_partition_by_kv_bytes_is_exact_and_balanced():
     rng = np.random.default_rng(5)
     lens = np.exp(rng.uniform(np.log(512), np.log(131072), 64)).astype(int)  # BASELINE config 5 lengths

@@ -13,7 +13,8 @@ import torch
 
 from qwengine_b200 import api
 from tests.gpu_util import dev_bf16, dev_bits, host_f32
-from tests.util import MAX_ABS, REL_L2, Case, rel_l2
+from oracle import pyoracle as O
+from tests.util import MAX_ABS, REL_L2, Case, bf16_floor, rel_l2
 
 pytestmark = pytest.mark.gpu
 
@@ -31,7 +32,14 @@ def _both(c, ctx, pos0, B):
     api.attn_decode_noalloc(q, kc, vc, got, dpos, 256, 4, 24, 1.0 / 16.0, ctx, B=B)
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
-    return host_f32(want), host_f32(got)
+    # and against the oracle itself, not only against the scratch-taking entry: attention of the given (already
+    # rotated) rows over the first pos0 + b + 1 cache rows, no gate; bf16 output, hence the rounding floor
+    ref, _ = O.mixer(c.q[:, :B], None, None, None, c.kc0.copy(), c.vc0.copy(), [pos0], do_rope=False, do_append=False,
+                     do_gate=False)
+    g = host_f32(got)
+    assert np.abs(g - ref).max() <= MAX_ABS
+    assert rel_l2(g, ref) <= float(np.hypot(REL_L2, bf16_floor(ref)))
+    return host_f32(want), g
 
 
 def test_noalloc_decode_matches_regular_entry_on_two_calls_in_a_row():
