@@ -41,11 +41,12 @@ FLOPS_PER_PAIR = 24576     # 4 * head_dim * q_heads per unmasked (query, key) pa
 
 
 def measured_peaks():
+    """(HBM GB/s, bf16 TFLOP/s burst, kind, bf16 TFLOP/s sustained under the power cap)."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
-    return 6650.0, 1590.0, "fallback"
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured", d.get("bf16_tflops_sustained", 1400.0)
+    return 6650.0, 1590.0, "fallback", 1400.0
 
 
 def recorded_traffic(kernel):
@@ -238,18 +239,18 @@ def bind_fused(api, w, flags_extra=0):
     return mx
 
 
-def kernel_time(api, step, steps, repeats):
+def kernel_time(api, step, n=10):
     """Duration of the step's dominant kernel: the library records an event pair around it on the launching
-    stream.  The pair sits between the step's two launches and so switches off their overlap; these steps are
-    therefore extra ones, taken right after the timed regions on the same buffers, and the figure is reported
-    beside ms_per_step, not instead of it."""
+    stream; n steps, each waited for before the next is launched (the kernel timed alone, as the peaks in
+    MEASURED_PEAKS.json were), median.  The pair sits between the step's two launches and so switches off their
+    overlap: these are extra steps, and the figure is reported beside ms_per_step, not instead of it."""
     ms = []
     api.profile_enable(True)
-    for _ in range(max(steps * repeats, 5)):
+    for _ in range(n):
         step()
         ms.append(api.profile_last_kernel_ms())
     api.profile_enable(False)
-    return float(np.mean(ms)), float(np.min(ms))
+    return float(np.median(ms))
 
 
 def measure(name, args, rank, world, flags_extra=0, with_e2e=True, fused_rows=False):
@@ -271,12 +272,16 @@ def measure(name, args, rank, world, flags_extra=0, with_e2e=True, fused_rows=Fa
         with_e2e = False
     steps = args.steps if w["n_new"] < 64 else max(3, min(args.steps, 20))
     warm = max(args.warmup, 3)
-    ms = timed(step, steps, warm, args.repeats, world)
+    for _ in range(warm):
+        step()
+    torch.cuda.synchronize()
     mx.check_status()
     launches = mx.launches()
     kernel = api.last_attention_kernel()
-    k_mean, k_min = kernel_time(api, step, steps, 1)
-    k_mean = rank_max([k_mean], world)[0]
+    k_alone = rank_max([kernel_time(api, step)], world)[0]              # the kernel timed alone, before the long regions
+    ms = timed(step, steps, warm, args.repeats, world)
+    k_after = rank_max([kernel_time(api, step, 5)], world)[0]           # and again right after them (clocks under the power cap)
+    k_mean = k_alone
 
     e2e_ms, h2d, d2h = None, 0, 0
     if with_e2e:
@@ -349,7 +354,7 @@ def measure(name, args, rank, world, flags_extra=0, with_e2e=True, fused_rows=Fa
     kv_all, flops_all = rank_sum([w["kv_bytes"], w["flops"]], world)
     return {"w": w, "steps": steps, "warmup": warm, "ms": ms, "ms_per_step": float(np.median(ms)),
             "e2e_ms": e2e_ms, "e2e_ms_per_step": float(np.median(e2e_ms)) if e2e_ms else None,
-            "kernel_ms": k_mean, "kernel": kernel, "kv_bytes_all": kv_all, "flops_all": flops_all,
+            "kernel_ms": k_mean, "kernel_ms_after": k_after, "kernel": kernel, "kv_bytes_all": kv_all, "flops_all": flops_all,
             "launches": launches * steps, "h2d": h2d, "d2h": d2h}
 
 
@@ -359,13 +364,14 @@ def describe(name, world, w):
             "sigmoid gate" % (name, w["n_seq_global"], n_new, hist))
 
 
-KERNEL_MS_HOW = ("CUDA event pair around the attention kernel on its stream, in extra steps right after the timed "
-                 "regions: the events sit between the step's two launches and switch their overlap off, so kernel_ms "
-                 "can exceed ms_per_step; frac_of_step uses ms_per_step instead")
+KERNEL_MS_HOW = ("CUDA event pair around the attention kernel on its stream: 10 extra steps before the timed regions, each "
+                 "waited for before the next (the kernel alone, as the measured peaks were taken), median.  The events sit "
+                 "between the step's two launches and switch their overlap off, so kernel_ms can exceed ms_per_step; "
+                 "frac_of_step uses ms_per_step (back-to-back steps, clocks as the power cap leaves them) instead")
 
 
 def hbm_roofline(algorithmic_bytes, kernel_ms, step_ms, kernel, peaks, world):
-    hbm_peak, _, kind = peaks
+    hbm_peak, _, kind = peaks[:3]
     achieved = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
     traffic, src = recorded_traffic(kernel) if world == 1 else (None, "captured on one GPU only")
     return {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
@@ -375,8 +381,8 @@ def hbm_roofline(algorithmic_bytes, kernel_ms, step_ms, kernel, peaks, world):
             "kernel": kernel, "kernel_ms": round(kernel_ms, 5), "kernel_ms_how": KERNEL_MS_HOW}
 
 
-def tensor_roofline(flops, kernel_ms, step_ms, kernel, peaks, world):
-    _, tc_peak, kind = peaks
+def tensor_roofline(flops, kernel_ms, step_ms, kernel, peaks, world, kernel_ms_after=None):
+    _, tc_peak, kind, tc_sustained = peaks
     achieved = flops / (kernel_ms * 1e-3) / 1e12
     traffic, src = recorded_traffic(kernel) if world == 1 else (None, "captured on one GPU only")
     return {"bound": "tensor", "achieved": round(achieved, 1), "peak": tc_peak, "unit": "TFLOP/s",
@@ -384,6 +390,11 @@ def tensor_roofline(flops, kernel_ms, step_ms, kernel, peaks, world):
             "frac_of_step": round(flops / (step_ms * 1e-3) / 1e12 / tc_peak, 4),
             "traffic": traffic, "traffic_source": src, "algorithmic_flops": flops, "peak_kind": kind,
             "kernel": kernel, "kernel_ms": round(kernel_ms, 5), "kernel_ms_how": KERNEL_MS_HOW,
+            "sustained": None if kernel_ms_after is None else {
+                "kernel_ms": round(kernel_ms_after, 5), "peak": tc_sustained,
+                "frac": round(flops / (kernel_ms_after * 1e-3) / 1e12 / tc_sustained, 4),
+                "what": "the same kernel right after the back-to-back regions, against the sustained (power-capped) "
+                        "cuBLAS figure of MEASURED_PEAKS.json"},
             "flops_counted": "4*256*24 per unmasked (query,key) pair; the bf16 lo pass of P is not counted"}
 
 
@@ -420,7 +431,7 @@ def tensor_line(name, r, world, peaks, mode):
         "config": {"workload": describe(name, world, w), "sharding": SHARDING[world], "p_operand": mode,
                    "l2_policy": "L2 flushed by the q/gate/out streams of the step (%.0f MB) plus KV"
                                 % (3 * w["q"].numel() * 2 / 1e6)},
-        "roofline": tensor_roofline(w["flops"], r["kernel_ms"], r["ms_per_step"], r["kernel"], peaks, world),
+        "roofline": tensor_roofline(w["flops"], r["kernel_ms"], r["ms_per_step"], r["kernel"], peaks, world, r["kernel_ms_after"]),
         "gpu_launches": r["launches"],
     }
     if r["e2e_ms_per_step"]:
@@ -502,22 +513,24 @@ def measure_dropin(args, peaks):
         api.attn_prefill(q, kc, vc, o, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, T)
         api.gate_sigmoid(o, gate, T * 24 * 256)
 
-    ms = timed(prefill_step, max(3, min(args.steps, 10)), 3, args.repeats, 1)
-    kernel = api.last_attention_kernel() if False else "prefill_umma_pair_kernel"
+    for _ in range(3):
+        prefill_step()
+    torch.cuda.synchronize()
     api.profile_enable(True)
     kms = []
-    for _ in range(5):
+    for _ in range(10):   # the attention kernel alone, each launch waited for, before the back-to-back regions
         api.attn_prefill(q, kc, vc, o, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, T)
         kms.append(api.profile_last_kernel_ms())
         kernel = api.last_attention_kernel()
     api.profile_enable(False)
+    ms = timed(prefill_step, max(3, min(args.steps, 10)), 3, args.repeats, 1)
     flops = float(T * pos0 + T * (T + 1) // 2) * FLOPS_PER_PAIR
     out["prefill_chunk"] = {
         "what": "one 2048-token chunk behind 30720 cached tokens: qw_rope x2, qw_kv_append, qw_attn_prefill, "
                 "qw_gate_sigmoid (bf16), as src/prefill.cu:142-156 launches them",
         "value": round(flops / (float(np.median(ms)) * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
         "ms_per_step": round(float(np.median(ms)), 5), "ms_per_step_stats": stats(ms), "gpu_launches_per_step": 5,
-        "roofline": tensor_roofline(flops, float(np.mean(kms)), float(np.median(ms)), kernel, peaks, 1)}
+        "roofline": tensor_roofline(flops, float(np.median(kms)), float(np.median(ms)), kernel, peaks, 1)}
     return out
 
 

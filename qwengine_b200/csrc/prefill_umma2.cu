@@ -55,6 +55,8 @@ struct PairCtl {
   uint32_t skip;                 // leader: the launch had already failed when this pair started
   float mxbuf[2][P2_NWG][128];
   float lbuf[P2_NWG][128];
+  float mbuf[128];
+  volatile int e_slot[2];       // by item parity: first ring slot the producer used for the item's epilogue tile
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -201,6 +203,15 @@ __device__ __forceinline__ bool pair_item(const PrefillParams &p, int k, int clu
   return true;
 }
 
+// First ring slot of the epilogue tile of the pair's k-th item, whose last KV tile is the pair's `tiles_through`-th.
+// The ring stream is  K_0 | K_1 V_0 | K_2 V_1 | ...  and an item's epilogue tile (two groups of two slots) follows
+// the V group of the item's last tile: before it the ring has seen one K and one V group per KV tile so far, the
+// K group of the next item's first tile if there is a next item, and two groups per earlier epilogue tile.  Its
+// four slots follow each other modulo the ring size.
+__device__ __forceinline__ int epi_tile_slot(int tiles_through, int k, bool has_next) {
+  return (4 * (tiles_through + k) + (has_next ? 2 : 0)) % P2_NSLOT;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P2_THREADS, 1)
 prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                          const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapG,
@@ -218,15 +229,17 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
 
   if (tid == 0) {
     mbar_init(&ctl->q_full, 1);
-    mbar_init(&ctl->q_ready, 2 * P2_SM_THREADS);
-    mbar_init(&ctl->o_drained, 2 * P2_SM_THREADS);
-    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_full[i], 2 * P2_SM_THREADS); }
+    // the softmax warps signal once per warp (a lane's tcgen05 / proxy fence, __syncwarp, then lane 0 arrives): a
+    // thousand arrivals per signal on one barrier, half of them from the other CTA, cost more than the work between them
+    mbar_init(&ctl->q_ready, 2 * (P2_SM_THREADS / 32));
+    mbar_init(&ctl->o_drained, 2 * (P2_SM_THREADS / 32));
+    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_full[i], 2 * (P2_SM_THREADS / 32)); }
     mbar_init(&ctl->o_done[0], 1);
     mbar_init(&ctl->o_done[1], 1);
     for (int i = 0; i < P2_NSLOT; ++i) mbar_init(&ctl->slot_full[i], 2);
     mbar_init(&ctl->fix_bar, 1);
     mbar_init(&ctl->g_full, 1);
-    mbar_init(&ctl->e_ready, P2_SM_THREADS);
+    mbar_init(&ctl->e_ready, P2_SM_THREADS / 32);
     mbar_init(&ctl->e_free, 1);
     ctl->abort_flag = 0;
     ctl->skip = (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) ? 1u : 0u;
@@ -254,11 +267,13 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
   const bool run = skip == 0;
 
   // The pair is persistent: it walks its items one after the other, and KV tiles are numbered through all of
-  // them (g = 0, 1, 2, ...).  Tile g uses S / P buffer g & 1 and barrier phase (g >> 1) & 1.  Inside an item
-  // the tensor pipe is fed  Q K_j^T, P V_{j-1}, Q K_{j+1}^T, P V_j, ...; at an item's end the last P V goes
-  // first, so that the softmax warps can start reading O out, and the next item's Q tile, its RoPE staging
-  // and its first two Q K^T products run while they do; only the next item's first P V waits for them
-  // (o_drained).  The ring follows the same order: ... K_last, V_last-1 | V_last, E, K'_0, K'_1, V'_0, K'_2, ...
+  // them (g = 0, 1, 2, ...).  Tile g uses S / P buffer g & 1 and barrier phase (g >> 1) & 1.  The tensor pipe is
+  // fed  Q K_g^T, P V_{g-1}, Q K_{g+1}^T, P V_g, ...  straight through the item boundaries: the first Q K^T of the
+  // next item runs before the last P V of this one, so the softmax warps can turn its scores into P while that
+  // last P V and the read-out of O are under way; only the next item's first P V waits, for O to have been read
+  // (o_drained).  The next item's Q tile is loaded as soon as this item's last Q K^T has retired and rotated by
+  // the softmax warps right after they have delivered this item's last P.  The ring follows the same order:
+  // ... K_last, V_last-1 | K'_0, V_last, E | K'_1, V'_0 | K'_2, ...
   //
   // E is the item's epilogue tile (bf16 output, p.tma_epi): four ring slots, one per 64-channel group, that the
   // producer fills with the item's gate tile by TMA; the softmax warps read their row's gate values from there,
@@ -358,6 +373,7 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
       for (int h2 = 0; h2 < 2 && ok; ++h2) {
         const int sl0 = next_group(3, k);
         if (sl0 < 0) return;
+        if (h2 == 0 && lane == 0) ctl->e_slot[k & 1] = sl0;   // read behind g_full, which orders it
         // g_full tells the softmax warps that the tile's slots are theirs: with a gate it completes when the
         // gate tile has landed, without one it is a plain arrival once both groups have been claimed
         if (elect_one()) {
@@ -374,15 +390,9 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         __syncwarp();
       }
     };
-    int k = 0;
-    for (; ok && pair_item(p, k, cluster, n_clusters, rank, w); ++k) {
-      // the previous item's last V tile comes first, as its P V does in the MMA thread; then its epilogue tile
-      if (pv_j >= 0) {
-        load_v(pv, pv_j, g - 1);
-        if (ok) load_e(pv, k - 1);
-        pv_j = -1;
-        if (!ok) break;
-      }
+    bool pv_last = false;  // the pending tile is the last of its item: its epilogue tile follows its V
+    int pv_k = 0;          // the pending tile's item
+    for (int k = 0; ok && pair_item(p, k, cluster, n_clusters, rank, w); ++k) {
       // this item's Q tile: the Q region is free once every Q K^T of the previous item has completed
       if (k > 0 && !__all_sync(0xffffffffu, wait_or_abort(&ctl->s_full[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag))) {
         producer_fail();
@@ -423,14 +433,19 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
           }
         }
         __syncwarp();
-        if (pv_j >= 0) load_v(pv, pv_j, g - 1);
+        if (pv_j >= 0) {   // V of the tile before (the previous item's last one when j = 0), then that item's epilogue tile
+          load_v(pv, pv_j, g - 1);
+          if (ok && pv_last) load_e(pv, pv_k);
+        }
         pv = w;
         pv_j = j;
+        pv_last = j == w.nt - 1;
+        pv_k = k;
       }
     }
     if (ok && pv_j >= 0) {
       load_v(pv, pv_j, g - 1);
-      if (ok) load_e(pv, k - 1);
+      if (ok && pv_last) load_e(pv, pv_k);
     }
   } else if (warp == 1) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(P2_CTL_REGS));
@@ -483,16 +498,9 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         }
         if (ok) umma_commit_both(&ctl->o_done[t & 1]);  // O updated; the tile's V slots are free
       };
+      bool pend_last = false;    // ... and the last of its item: that item's epilogue tile follows its V in the ring
       PairItem w;
       for (int k = 0; ok && pair_item(p, k, cluster, n_clusters, rank, w); ++k) {
-        // The last P V of the previous item goes first: the softmax warps start reading O out as soon as
-        // it retires, and the two Q K^T products below keep the pipe busy meanwhile.
-        if (pend) {
-          issue_pv(g - 1, pend_first, pend_item);
-          pend = false;
-          if (p.tma_epi) it += 4;  // the previous item's epilogue tile sits in the ring here
-        }
-        if (!ok) break;
         if (!wait_cluster_or_abort(&ctl->q_ready, k & 1, abort_flag)) { fail(DEV_ERR_MMA_WAIT); break; }
         tc_fence_after();
         for (int j = 0; j < w.nt && ok; ++j, ++g) {
@@ -524,11 +532,15 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
           // one completion point for the whole S tile, seen by the softmax warps (S is ready) and
           // by both producers (the tile's K slots are free)
           umma_commit_both(&ctl->s_full[g & 1]);
-          // ---- O += P V of the tile before (the previous item's last one was issued above) ----
-          if (pend) issue_pv(g - 1, pend_first, pend_item);
+          // ---- O (+)= P V of the tile before; at j = 0 that is the previous item's last tile ----
+          if (pend) {
+            issue_pv(g - 1, pend_first, pend_item);
+            if (pend_last && p.tma_epi) it += 4;  // that item's epilogue tile sits in the ring here
+          }
           pend = true;
           pend_first = j == 0;
           pend_item = k;
+          pend_last = j == w.nt - 1;
         }
       }
       if (ok && pend) issue_pv(g - 1, pend_first, pend_item);
@@ -541,17 +553,19 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
     // slots to the ring.  A tile that reaches past the chunk's end was stored row by row by the softmax warps
     // (a TMA store would overwrite the rows that follow): its slots are returned as they are.
     if (warp == 2 && run && p.tma_epi) {
-      PairItem w;
+      PairItem w, wn;
       int G = 0;
-      for (int k = 0; pair_item(p, k, cluster, n_clusters, rank, w); ++k) {
+      bool have = pair_item(p, 0, cluster, n_clusters, rank, w);
+      for (int k = 0; have; ++k) {
+        const bool has_next = pair_item(p, k + 1, cluster, n_clusters, rank, wn);
         if (!__all_sync(0xffffffffu, wait_or_abort(&ctl->e_ready, k & 1, abort_flag))) break;
         if (elect_one()) {
           if (w.rows_valid == P2_BM) {
-            const int base = (4 * (G + w.nt + k)) % P2_NSLOT;
+            const int base = epi_tile_slot(G + w.nt, k, has_next);
             const int qrow = w.s * p.n_new + w.q0;
 #pragma unroll
             for (int c = 0; c < 4; ++c)
-              tma_store_2d(&mapO, ring + (size_t)(base + c) * P2_SLOT, w.head * HEAD_DIM + c * 64, qrow);
+              tma_store_2d(&mapO, ring + (size_t)((base + c) % P2_NSLOT) * P2_SLOT, w.head * HEAD_DIM + c * 64, qrow);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           }
@@ -559,6 +573,8 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         }
         __syncwarp();
         G += w.nt;
+        have = has_next;
+        w = wn;
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every store has landed before the CTA may exit
     }
@@ -612,8 +628,9 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         *reinterpret_cast<uint4 *>(lo_base + ((c ^ (row & 7)) << 4)) = make_uint4(xl[0], xl[1], xl[2], xl[3]);
         *reinterpret_cast<uint4 *>(lo_base + (((c + 4) ^ (row & 7)) << 4)) = make_uint4(yl[0], yl[1], yl[2], yl[3]);
       }
-      fence_proxy_async();
-      remote_arrive_release(q_ready_addr);
+      fence_proxy_async();   // each lane publishes its rows to the tensor core's proxy; then one arrival per warp
+      __syncwarp();
+      if (lane == 0) remote_arrive_release(q_ready_addr);
     };
 
     int o_seen = 0;  // P V completions observed so far, in order (tile t: o_done[t & 1], phase t / 2)
@@ -623,11 +640,97 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         ++o_seen;
       }
     };
+    // End of an item: 1/l, gate, store.  O is read out of tensor memory, a row per thread, 64 channels per
+    // warpgroup.  With an epilogue tile in the ring (bf16 output, a full tile of 128 rows) the row's gate values
+    // are read from shared memory and the gated output is written over them for the TMA store; otherwise
+    // (fp32 output, or a tile that reaches past the chunk's last row) gate and output move by plain loads and
+    // stores, one 128-byte run per thread.
+    // kf: the finished item (the pair's kf-th); tiles_through: KV tiles of the pair up to and including its last.
+    // The item's row sums and maxima were left in lbuf / mbuf when the softmax warps moved on to the next item.
+    auto epilogue = [&](int kf, int tiles_through, bool has_next) {
+      PairItem f;
+      pair_item(p, kf, cluster, n_clusters, rank, f);
+      const bool live_row = row < f.rows_valid;
+      const bool via_tile = p.tma_epi && f.rows_valid == P2_BM;
+      const size_t grow = ((size_t)f.s * p.n_new + f.q0 + row) * p.q_heads + f.head;
+      const size_t elem0 = grow * HEAD_DIM + wg * 64;
+      const uint4 *gp = reinterpret_cast<const uint4 *>(p.gate + elem0);
+      if (!via_tile && p.gate && live_row) asm volatile("prefetch.global.L2 [%0];" ::"l"(gp));
+      // this warpgroup's slot of the epilogue tile
+      uint8_t *e_row = ring + (size_t)((epi_tile_slot(tiles_through, kf, has_next) + wg) % P2_NSLOT) * P2_SLOT + row * 128;
+      wait_pv_done(tiles_through - 1);
+      if (ok && p.tma_epi) ok = wait_or_abort(&ctl->g_full, kf & 1, abort_flag);  // the epilogue tile is ours (and holds the gate)
+      asm volatile("bar.sync 1, %0;" ::"n"(P2_SM_THREADS) : "memory");
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0 && !*abort_flag && p.status) *p.status = DEV_ERR_SOFTMAX_WAIT;
+        *abort_flag = 1;
+        ok = false;
+        return;
+      }
+      tc_fence_after();
+      float l_tot = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < P2_NWG; ++w2) l_tot += ctl->lbuf[w2][row];
+      const float m_row = ctl->mbuf[row];
+      // lbuf / mbuf are single buffers: nobody may run on to the end of the next item (a one-tile item ends right
+      // after this epilogue) and overwrite them before every thread has read its row
+      asm volatile("bar.sync 1, %0;" ::"n"(P2_SM_THREADS) : "memory");
+      const float inv = 1.f / l_tot;
+      const uint32_t t_o = tmem + lane_sel + TMEM_O + wg * 64;
+      // both halves of the row's 64 channels go to registers first: the accumulator is then free for the next
+      // item's first P V while the gate arithmetic below runs
+      uint32_t orow[2][32];
+      tmem_ld32(t_o, orow[0]);
+      tmem_ld32(t_o + 32, orow[1]);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) remote_arrive(o_drained_addr);
+      // the producer's ring bookkeeping and the arithmetic above must agree on where the tile is
+      if (p.tma_epi && ctl->e_slot[kf & 1] != epi_tile_slot(tiles_through, kf, has_next)) {
+        if (!*abort_flag && p.status) *p.status = DEV_ERR_RING;
+        *abort_flag = 1;
+        ok = false;
+        return;
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        if (via_tile || live_row) {
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8) {
+            float o8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(orow[c][v8 * 8 + e]) * inv;
+            if (p.gate) {
+              const uint4 gv = via_tile ? *reinterpret_cast<const uint4 *>(e_row + (((c * 4 + v8) ^ (row & 7)) << 4)) : __ldg(gp + c * 4 + v8);
+              const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                o8[2 * e] *= sigmoid_tanh(bf16lo(gw[e]));
+                o8[2 * e + 1] *= sigmoid_tanh(bf16hi(gw[e]));
+              }
+            }
+            if (via_tile)
+              *reinterpret_cast<uint4 *>(e_row + (((c * 4 + v8) ^ (row & 7)) << 4)) =
+                  make_uint4(pack_bf16(o8[0], o8[1]), pack_bf16(o8[2], o8[3]), pack_bf16(o8[4], o8[5]), pack_bf16(o8[6], o8[7]));
+            else if (p.out_is_f32) store8<float>(reinterpret_cast<float *>(p.out) + elem0 + c * 32 + v8 * 8, o8);
+            else store8<uint16_t>(reinterpret_cast<uint16_t *>(p.out) + elem0 + c * 32 + v8 * 8, o8);
+          }
+        }
+      }
+      if (p.tma_epi) {  // the tile (written or not) goes back to the warp that stores it and frees its slots
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->e_ready);
+      }
+
+      if (wg == 0 && live_row && p.lse) p.lse[grow] = (m_row + log2f(l_tot)) * LN2;
+    };
     int G = 0;  // KV tiles of the items before the current one
     PairItem w;
     bool have = pair_item(p, 0, cluster, n_clusters, rank, w);
     if (have) stage_q(w, 0);
-    for (int k = 0; have; ++k) {
+    for (int k = 0; have && ok; ++k) {
       const int nt = w.nt, pos = w.pos, q0 = w.q0;
       const int qpos = pos + q0 + row;  // causal limit: keys 0 .. qpos
       float m_used = -INFINITY, l_run = 0.f;
@@ -701,90 +804,27 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
         l_run += lsum;
         tmem_wait_st();
         tc_fence_before();
-        remote_arrive(p_full_addr[g & 1]);
+        __syncwarp();
+        if (lane == 0) remote_arrive(p_full_addr[g & 1]);
         // Last tile of the item: every Q K^T of it has completed (s_full above), so the producer has already
         // asked for the next item's Q tile -- rotate it while the tensor core runs this item's last P V.
         if (j == nt - 1) {
           PairItem wn;  // looked up again at the item's end rather than kept in registers through the epilogue
           if (pair_item(p, k + 1, cluster, n_clusters, rank, wn)) stage_q(wn, k + 1);
         }
+        // The first P of this item is on its way: now finish the previous item (its last P V was issued right
+        // after this item's first Q K^T).  This item's first P V waits until O has been read out.
+        if (j == 0 && k > 0) epilogue(k - 1, G, true);
         if (j > 0) wait_pv_done(g - 1);
       }
-
-      // ---- end of the item: 1/l, gate, store.  O is read out of tensor memory, a row per thread, 64 channels per
-      // warpgroup.  With an epilogue tile in the ring (bf16 output, a full tile of 128 rows) the row's gate values
-      // are read from shared memory and the gated output is written over them for the TMA store; otherwise
-      // (fp32 output, or a tile that reaches past the chunk's last row) gate and output move by plain loads and
-      // stores, one 128-byte run per thread. ----
+      // the row's sum and maximum wait in shared memory for the item's epilogue (single buffers: the epilogue of
+      // the item before has run by now, at this item's first tile)
       ctl->lbuf[wg][row] = l_run;
-      const bool live_row = row < w.rows_valid;
-      const bool via_tile = p.tma_epi && w.rows_valid == P2_BM;
-      const size_t grow = ((size_t)w.s * p.n_new + q0 + row) * p.q_heads + w.head;
-      const size_t elem0 = grow * HEAD_DIM + wg * 64;
-      const uint4 *gp = reinterpret_cast<const uint4 *>(p.gate + elem0);
-      if (!via_tile && p.gate && live_row) asm volatile("prefetch.global.L2 [%0];" ::"l"(gp));
-      // this warpgroup's slot of the epilogue tile: the ring groups before it are two per KV tile so far and two
-      // per earlier item
-      uint8_t *e_row = ring + (size_t)((4 * (G + nt + k) + wg) % P2_NSLOT) * P2_SLOT + row * 128;
-      wait_pv_done(G + nt - 1);
-      if (ok && p.tma_epi) ok = wait_or_abort(&ctl->g_full, k & 1, abort_flag);  // the epilogue tile is ours (and holds the gate)
-      asm volatile("bar.sync 1, %0;" ::"n"(P2_SM_THREADS) : "memory");
-      if (!__all_sync(0xffffffffu, ok)) {
-        if (lane == 0 && !*abort_flag && p.status) *p.status = DEV_ERR_SOFTMAX_WAIT;
-        *abort_flag = 1;
-        break;
-      }
-      tc_fence_after();
-      float l_tot = 0.f;
-#pragma unroll
-      for (int w2 = 0; w2 < P2_NWG; ++w2) l_tot += ctl->lbuf[w2][row];
-      const float inv = 1.f / l_tot;
-      const uint32_t t_o = tmem + lane_sel + TMEM_O + wg * 64;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t orow[32];
-        uint4 gq[4];
-        tmem_ld32(t_o + c * 32, orow);
-        if (p.gate && (via_tile || live_row)) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            gq[i] = via_tile ? *reinterpret_cast<const uint4 *>(e_row + (((c * 4 + i) ^ (row & 7)) << 4)) : __ldg(gp + c * 4 + i);
-        }
-        tmem_wait_ld();
-        if (c == 1) {  // O is in registers: the next item's first P V may overwrite the accumulator
-          tc_fence_before();
-          remote_arrive(o_drained_addr);
-        }
-        if (via_tile || live_row) {
-#pragma unroll
-          for (int v8 = 0; v8 < 4; ++v8) {
-            float o8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(orow[v8 * 8 + e]) * inv;
-            if (p.gate) {
-              const uint4 gv = gq[v8];
-              const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                o8[2 * e] *= sigmoid_fast(bf16lo(gw[e]));
-                o8[2 * e + 1] *= sigmoid_fast(bf16hi(gw[e]));
-              }
-            }
-            if (via_tile)
-              *reinterpret_cast<uint4 *>(e_row + (((c * 4 + v8) ^ (row & 7)) << 4)) =
-                  make_uint4(pack_bf16(o8[0], o8[1]), pack_bf16(o8[2], o8[3]), pack_bf16(o8[4], o8[5]), pack_bf16(o8[6], o8[7]));
-            else if (p.out_is_f32) store8<float>(reinterpret_cast<float *>(p.out) + elem0 + c * 32 + v8 * 8, o8);
-            else store8<uint16_t>(reinterpret_cast<uint16_t *>(p.out) + elem0 + c * 32 + v8 * 8, o8);
-          }
-        }
-      }
-      if (p.tma_epi) {  // the tile (written or not) goes back to the warp that stores it and frees its slots
-        fence_proxy_async();
-        mbar_arrive(&ctl->e_ready);
-      }
-      if (wg == 0 && live_row && p.lse) p.lse[grow] = (m_used + log2f(l_tot)) * LN2;
+      if (wg == 0) ctl->mbuf[row] = m_used;
+
       G += nt;
       have = pair_item(p, k + 1, cluster, n_clusters, rank, w);
+      if (!have && ok) epilogue(k, G, false);   // the pair's last item
     }
   }
 

@@ -83,11 +83,13 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   const int cta = blockIdx.x;
 
   if (tid == 0) {
-    mbar_init(&ctl->q_ready, DU_SM_THREADS);
-    mbar_init(&ctl->o_free, DU_SM_THREADS);
+    // the softmax warps signal once per warp (each lane's fence, __syncwarp, then lane 0 arrives): 512 arrivals on
+    // one barrier per signal cost more than the work between two signals
+    mbar_init(&ctl->q_ready, DU_SM_THREADS / 32);
+    mbar_init(&ctl->o_free, DU_SM_THREADS / 32);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ctl->s_full[i], 1);
-      mbar_init(&ctl->p_full[i], DU_SM_THREADS);
+      mbar_init(&ctl->p_full[i], DU_SM_THREADS / 32);
       mbar_init(&ctl->o_done[i], 1);
     }
     for (int i = 0; i < DU_MAX_SLOT; ++i) { mbar_init(&ctl->slot_full[i], 1); mbar_init(&ctl->slot_empty[i], 1); }
@@ -373,7 +375,8 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
         }
       }
       fence_proxy_async();
-      mbar_arrive(&ctl->q_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->q_ready);
     };
     // units cut across CTAs: their merge is settled after this CTA's last tile
     int pend_u[2] = {0, 0}, pend_nt[2] = {0, 0}, n_pend = 0;
@@ -489,7 +492,8 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           fence_proxy_async();
         }
         tc_fence_before();
-        mbar_arrive(&ctl->p_full[Jt & 1]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->p_full[Jt & 1]);
         // Last tile of the segment: every Q K^T of this unit has completed (s_full above), so the Q
         // tile is free -- stage the next unit's rows while the tensor core runs this tile's P V.
         if (j == t1 - 1 && have_next) stage_q(unit_info(p, u_next));
@@ -551,7 +555,8 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       }
       // O has been read (or is abandoned): the next segment's first P V may overwrite it
       tc_fence_before();
-      mbar_arrive(&ctl->o_free);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->o_free);
       if (!all_ok) {
         if (lane == 0) fail(DEV_ERR_SOFTMAX_WAIT);
         break;
