@@ -218,25 +218,29 @@ __device__ __forceinline__ void merge_finish(const SplitKVParams &p, const UnitI
 // of the unit, in CTA order (fixed order => bit-stable), then normalises, gates and stores.
 // One warp per row, lane = 8 channels.  Used by the merge kernel and, when arrival counters are
 // available, by whichever CTA finishes the unit last.
-template <typename TOut>
+template <typename TOut, int BATCH = 4>
 __device__ __forceinline__ void merge_unit_row(const SplitKVParams &p, int u, const UnitInfo &ui, int row, int c_first,
                                                int c_last, long long total, int lane, int G,
                                                const volatile uint8_t *live_of = nullptr) {
-  // Partials are fetched four at a time with all their loads in flight together (a unit is
-  // usually cut into two to four pieces, so this is one L2 round trip) and folded in with a
-  // running maximum, strictly in CTA order.
+  // Partials are fetched BATCH at a time with all their loads in flight together (a unit is
+  // usually cut into two to four pieces, so this is one L2 round trip; one sequence alone is cut
+  // into dozens, and the merge is then a chain of round trips: hence eight at a time there) and
+  // folded in with a running maximum, strictly in CTA order.
+  // When there are at least as many tiles as CTAs every CTA owns tiles, so every CTA between the
+  // unit's first and last has written a part: the per-CTA test (two 64-bit divisions) is skipped.
+  const bool all_live = total >= (long long)G;
   float mg = -INFINITY, lg = 0.f;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int c0 = c_first; c0 <= c_last; c0 += 4) {
-    float mv[4], lv[4];
-    float4 av[4], bv[4];
-    bool live[4];
+  for (int c0 = c_first; c0 <= c_last; c0 += BATCH) {
+    float mv[BATCH], lv[BATCH];
+    float4 av[BATCH], bv[BATCH];
+    bool live[BATCH];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < BATCH; ++k) {
       const int c = c0 + k;
       // CTAs without tiles wrote nothing; live_of, when given, holds that test for c_first .. c_last
       // (64-bit divisions are slow enough to dominate a merge of many parts)
-      live[k] = c <= c_last && (live_of ? live_of[c - c_first] != 0 : (total * c / G != total * (c + 1) / G));
+      live[k] = c <= c_last && (all_live || (live_of ? live_of[c - c_first] != 0 : (total * c / G != total * (c + 1) / G)));
       const float *src = p.ws + ((size_t)((live[k] ? c : c_first) + u) * (p.rb * GROUP) + row) * PART_STRIDE;
       mv[k] = __ldcg(src + 256);
       lv[k] = __ldcg(src + 257);
@@ -244,7 +248,7 @@ __device__ __forceinline__ void merge_unit_row(const SplitKVParams &p, int u, co
       bv[k] = __ldcg(reinterpret_cast<const float4 *>(src + lane * 8 + 4));
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < BATCH; ++k) {
       if (!live[k] || !(lv[k] > 0.f)) continue;
       const float m_new = fmaxf(mg, mv[k]);
       const float f_old = fast_exp2(mg - m_new), f = fast_exp2(mv[k] - m_new);  // mg = -inf gives f_old = 0
@@ -257,6 +261,14 @@ __device__ __forceinline__ void merge_unit_row(const SplitKVParams &p, int u, co
     }
   }
   merge_finish<TOut>(p, ui, row, lane, mg, lg, acc);
+}
+
+// The same with eight parts in flight, as a function of its own: inlined, its registers would be taken out of the
+// budget of the kernel's tile loop (168 per thread with the nine-warp block), which then spills.
+template <typename TOut>
+__device__ __noinline__ void merge_unit_row_wide(const SplitKVParams &p, int u, const UnitInfo &ui, int row, int c_first,
+                                                 int c_last, long long total, int lane, int G) {
+  merge_unit_row<TOut, 8>(p, u, ui, row, c_first, c_last, total, lane, G);
 }
 
 // FOLD = false: a dedicated producer warp (warp NCW).  FOLD = true: lane 0 of consumer warp 0 also
@@ -765,9 +777,15 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       }
       consumer_sync(NCT);
       const int c_first = cta_of_tile(pre, total, G), c_last = cta_of_tile(pre + nt_unit - 1, total, G);
-      int nparts = 0;
-      for (int c = c_first; c <= c_last; ++c) nparts += (total * c / G != total * (c + 1) / G) ? 1 : 0;
+      // how many CTAs hold a part of the unit: all of c_first .. c_last when there are at least as many tiles as
+      // CTAs (the usual case); otherwise count the ones that own tiles (two 64-bit divisions each: slow)
+      int nparts = c_last - c_first + 1;
+      if (total < (long long)G) {
+        nparts = 0;
+        for (int c = c_first; c <= c_last; ++c) nparts += (total * c / G != total * (c + 1) / G) ? 1 : 0;
+      }
       if (*ticket == nparts - 1) {
+        // a unit cut into more than four parts (one sequence alone is cut into dozens) is merged eight parts at a time
         for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, G);
         if (tid == 0) p.cnt[u] = 0;  // leave the counter clean for a caller that does not reset it
       }
@@ -799,7 +817,7 @@ __global__ void __launch_bounds__(256) splitkv_merge_kernel(const __grid_constan
   const int c_first = cta_of_tile(pre, total, G), c_last = cta_of_tile(pre + nt - 1, total, G);
   if (c_first == c_last) return;  // the main kernel already wrote this unit
   const int R = ui.ntok * GROUP;
-  for (int row = warp; row < R; row += 8) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, G);
+  for (int row = warp; row < R; row += 8) merge_unit_row_wide<TOut>(p, u, ui, row, c_first, c_last, total, lane, G);
 }
 
 // Merge n_parts partial sets [n_parts][n][PART_STRIDE] (n = rows * q_heads) in index order, then
