@@ -146,7 +146,7 @@ static void new_rows(Site &s, int B) {  // what the projections + QK-norm would 
 }
 static void set_pos(Site &s, int pos) { CK(cudaMemcpy(s.dpos, &pos, 4, cudaMemcpyHostToDevice)); }
 
-// src/model.cu:228-240 with the launches replaced as INTEGRATION.md shows
+// src/model.cu:228-240 with each launch replaced by its mixer.hpp counterpart
 static void record_step_ours(Site &s, int B, cudaStream_t st) {
   const float scale = 1.0f / sqrtf((float)HEAD_DIM);
   QW(qw::rope(s.qh, N_Q_HEADS, HEAD_DIM, ROTARY_DIM, s.dpos, ROPE_THETA, st, B));

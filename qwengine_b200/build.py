@@ -36,13 +36,30 @@ def needs_build():
 
 
 def build(force=False, verbose=False):
+    """Compiles the library if a source is newer than it.  Safe when several processes (one rank per GPU) call it
+    at once: one of them compiles under a file lock into a temporary name and renames it into place, the others
+    wait for the lock and find the library up to date."""
     if not force and not needs_build():
         return LIB
-    r = subprocess.run(nvcc_cmd(verbose), capture_output=True, text=True)
-    if verbose or r.returncode:
-        sys.stderr.write(r.stdout + r.stderr)
-    if r.returncode:
-        raise RuntimeError("nvcc failed building libqwengine_attn.so")
+    import fcntl
+    with open(LIB + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not needs_build():
+                return LIB
+            tmp = "%s.%d.tmp" % (LIB, os.getpid())
+            cmd = nvcc_cmd(verbose)
+            cmd[cmd.index("-o") + 1] = tmp
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if verbose or r.returncode:
+                sys.stderr.write(r.stdout + r.stderr)
+            if r.returncode:
+                if os.path.exists(tmp):
+                    os.remove(tmp)
+                raise RuntimeError("nvcc failed building libqwengine_attn.so")
+            os.replace(tmp, LIB)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB
 
 

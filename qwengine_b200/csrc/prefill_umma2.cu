@@ -6,22 +6,36 @@
 // is split across the pair's shared memories -- for S = Q K^T each CTA stages 64 of the tile's 128
 // keys, for O += P V each CTA stages 128 of the 256 value channels.  Per CTA and KV tile that is
 // 64 KB instead of 128 KB: half the L2->SM traffic, half the shared-memory read bandwidth per MMA,
-// and the same 128 KB ring now holds two tiles of look-ahead instead of one, which is what hides
-// the load latency the single-CTA kernel is bound by.
+// and the same 128 KB ring holds two tiles of look-ahead instead of one.
 //
-// TMEM map: O | S0 | S1, P over
-// S as bf16 hi + lo; warp roles (0 = TMA producer, 1 = TMEM owner and -- in the leader CTA only --
-// MMA issuer, 2..17 = four softmax warpgroups), RoPE(q) prologue in shared memory, 1/l * sigmoid
-// epilogue out of TMEM, bounded waits with an abort flag and a status word.
+// TMEM map: O | S0 | S1, P over S as bf16 hi + lo.
+//
+// The kernel is persistent: the grid is as many CTA pairs as the device holds at once and each
+// pair walks a static list of items (sequence, query tile, head pair) dealt out heaviest first in
+// rounds of alternating direction.  KV tiles are numbered through all items of a pair; the MMA
+// stream is Q K_g^T, P V_{g-1}, Q K_{g+1}^T, ... straight through item boundaries and the K/V ring
+// is filled in that same order.
+//
+// Warp roles: a control warpgroup (warp 0 = TMA producer, warp 1 = TMEM owner and -- in the leader
+// CTA only -- MMA issuer, warp 2 = TMA store of finished output tiles, warp 3 idle) that gives
+// registers away with setmaxnreg, and four softmax warpgroups (thread = query row x 32-key group)
+// that take them.  The softmax warps also rotate the next item's Q tile in shared memory (RoPE,
+// hi + lo sub-tiles) after delivering the current item's last P, and finish the PREVIOUS item
+// (O out of TMEM, 1/l, sigmoid gate) after delivering the next item's first P, so the tensor pipe
+// has work across the boundary.  The epilogue tile of an item lives in four ring slots behind the
+// item's last V tile: the producer loads the gate rows there by TMA, the softmax warps overwrite
+// them with the gated output, the store warp sends them out by TMA and returns the slots.
+// Every wait is bounded; on expiry the CTA raises an abort flag and writes a status word.
 //
 // Cross-CTA signalling: the leader's barriers collect both CTAs.  TMA loads of either CTA complete
 // on the leader's slot barrier (cp.async.bulk.tensor with .cta_group::2, no multicast); softmax
-// threads of the peer arrive on the leader's q_ready / p_full barriers through mapa'd addresses;
-// the MMA thread publishes "S_j complete" and "P_j V_j retired" to both CTAs with one
-// tcgen05.commit each (arrival multicast to the same barrier in both CTAs); those two signals also
-// free the ring slots: K slots are reused every second tile and V slots every second tile, so the
-// producers wait for s_full / o_done of the tile that last used the slot instead of per-slot
-// barriers.
+// warps of the peer arrive (one arrival per warp) on the leader's q_ready / p_full / o_drained
+// barriers through mapa'd addresses; the MMA thread publishes "S_g complete" and "P_g V_g retired"
+// to both CTAs with one tcgen05.commit each (arrival multicast to the same barrier in both CTAs).
+// Those two signals also free the ring: the producer remembers the last occupant of each slot
+// group and waits for exactly the completion that releases it (s_full for a K group, o_done for a
+// V group, e_free for an epilogue tile), every completion observed in tile order because a parity
+// wait cannot tell two phases apart.
 //
 #include "prefill_umma.cuh"
 
@@ -41,7 +55,7 @@ constexpr int P2_NSLOT = 8;                // ring slots: 2 K + 2 V per tile -> 
 constexpr int P2_QBYTES = 5 * P2_SLOT;     // four 64-channel Q sub-tiles + the rotary "lo" sub-tile
 constexpr int P2_NWG = 4;
 constexpr int P2_SM_THREADS = P2_NWG * 128;
-constexpr int P2_CTL_THREADS = 128;         // control warpgroup: TMA producer, MMA issuer, two idle warps
+constexpr int P2_CTL_THREADS = 128;         // control warpgroup: TMA producer, MMA issuer, output-store warp, one idle warp
 constexpr int P2_THREADS = P2_CTL_THREADS + P2_SM_THREADS;
 constexpr int P2_CTL_REGS = 64, P2_SM_REGS = 104;  // after setmaxnreg: 128 x 64 + 512 x 104 = the 640 x 96 registers the block starts with
 
