@@ -21,6 +21,7 @@ timed region is `steps` back-to-back steps between CUDA events, repeated `repeat
 figures are the median (and min / max) over the repeats of the slowest rank's time.
 """
 import argparse
+import datetime
 import hashlib
 import json
 import os
@@ -852,7 +853,10 @@ def run_ours(args, rank, local_rank, world):
     ex_cls = None
     if world > 1:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads only: no multicast binding
-        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # a short collective timeout: ranks that stop agreeing on the next collective end with an error within
+        # minutes instead of holding eight GPUs for the default ten
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                             timeout=datetime.timedelta(seconds=180))
         from qwengine_b200 import sharding
         ex_cls = sharding.PeerExchange
     peaks = measured_peaks()
