@@ -50,15 +50,18 @@ def measured_peaks():
     return 6650.0, 1590.0, "fallback", 1400.0
 
 
-def recorded_traffic(kernel):
+def recorded_traffic(kernel, workload=None):
     """DRAM bytes per launch of `kernel` from the committed ncu capture (profiles/traffic.json), or None with a
-    reason when the kernel's sources have changed since the capture (the figure would be stale)."""
+    reason when the kernel's sources have changed since the capture (the figure would be stale) or the capture
+    was of another workload than the one being reported."""
     p = os.path.join(ROOT, "profiles", "traffic.json")
     if not os.path.exists(p):
         return None, "no profiles/traffic.json"
     e = json.load(open(p)).get(kernel)
     if not e:
         return None, "no capture of this kernel recorded"
+    if workload is not None and not e.get("workload", "").startswith(workload + ":"):
+        return None, "the recorded capture is of another workload (%s)" % e.get("workload", "?")
     h = hashlib.sha256()
     for f in e["sources"]:
         with open(os.path.join(ROOT, "qwengine_b200", "csrc", f), "rb") as fh:
@@ -371,10 +374,10 @@ KERNEL_MS_HOW = ("CUDA event pair around the attention kernel on its stream: 10 
                  "frac_of_step uses ms_per_step (back-to-back steps, clocks as the power cap leaves them) instead")
 
 
-def hbm_roofline(algorithmic_bytes, kernel_ms, step_ms, kernel, peaks, world):
+def hbm_roofline(algorithmic_bytes, kernel_ms, step_ms, kernel, peaks, world, workload=None):
     hbm_peak, _, kind = peaks[:3]
     achieved = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
-    traffic, src = recorded_traffic(kernel) if world == 1 else (None, "captured on one GPU only")
+    traffic, src = recorded_traffic(kernel, workload) if world == 1 else (None, "captured on one GPU only")
     return {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
             "frac": round(achieved / hbm_peak, 4),
             "frac_of_step": round(algorithmic_bytes / (step_ms * 1e-3) / 1e9 / hbm_peak, 4),
@@ -382,10 +385,10 @@ def hbm_roofline(algorithmic_bytes, kernel_ms, step_ms, kernel, peaks, world):
             "kernel": kernel, "kernel_ms": round(kernel_ms, 5), "kernel_ms_how": KERNEL_MS_HOW}
 
 
-def tensor_roofline(flops, kernel_ms, step_ms, kernel, peaks, world, kernel_ms_after=None):
+def tensor_roofline(flops, kernel_ms, step_ms, kernel, peaks, world, kernel_ms_after=None, workload=None):
     _, tc_peak, kind, tc_sustained = peaks
     achieved = flops / (kernel_ms * 1e-3) / 1e12
-    traffic, src = recorded_traffic(kernel) if world == 1 else (None, "captured on one GPU only")
+    traffic, src = recorded_traffic(kernel, workload) if world == 1 else (None, "captured on one GPU only")
     return {"bound": "tensor", "achieved": round(achieved, 1), "peak": tc_peak, "unit": "TFLOP/s",
             "frac": round(achieved / tc_peak, 4),
             "frac_of_step": round(flops / (step_ms * 1e-3) / 1e12 / tc_peak, 4),
@@ -409,7 +412,7 @@ def hbm_line(name, r, world, peaks):
         "dtype": "bf16", "data": "synthetic: seeded N(0,1) bf16 q/k/v/gate and KV cache, no dataset",
         "config": {"workload": describe(name, world, w), "sharding": SHARDING[world],
                    "l2_policy": "inputs larger than L2: %.0f MB of KV per GPU per step vs 126 MB L2" % (w["kv_bytes"] / 1e6)},
-        "roofline": hbm_roofline(w["kv_bytes"], r["kernel_ms"], r["ms_per_step"], r["kernel"], peaks, world),
+        "roofline": hbm_roofline(w["kv_bytes"], r["kernel_ms"], r["ms_per_step"], r["kernel"], peaks, world, name),
         "gpu_launches": r["launches"],
     }
     if r["e2e_ms_per_step"]:
@@ -432,7 +435,7 @@ def tensor_line(name, r, world, peaks, mode):
         "config": {"workload": describe(name, world, w), "sharding": SHARDING[world], "p_operand": mode,
                    "l2_policy": "L2 flushed by the q/gate/out streams of the step (%.0f MB) plus KV"
                                 % (3 * w["q"].numel() * 2 / 1e6)},
-        "roofline": tensor_roofline(w["flops"], r["kernel_ms"], r["ms_per_step"], r["kernel"], peaks, world, r["kernel_ms_after"]),
+        "roofline": tensor_roofline(w["flops"], r["kernel_ms"], r["ms_per_step"], r["kernel"], peaks, world, r["kernel_ms_after"], name),
         "gpu_launches": r["launches"],
     }
     if r["e2e_ms_per_step"]:
@@ -531,7 +534,7 @@ def measure_dropin(args, peaks):
                 "qw_gate_sigmoid (bf16), as src/prefill.cu:142-156 launches them",
         "value": round(flops / (float(np.median(ms)) * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
         "ms_per_step": round(float(np.median(ms)), 5), "ms_per_step_stats": stats(ms), "gpu_launches_per_step": 5,
-        "roofline": tensor_roofline(flops, float(np.median(kms)), float(np.median(ms)), kernel, peaks, 1)}
+        "roofline": tensor_roofline(flops, float(np.median(kms)), float(np.median(ms)), kernel, peaks, 1, workload="prefill_chunk")}
     return out
 
 
