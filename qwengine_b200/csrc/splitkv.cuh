@@ -271,6 +271,144 @@ __device__ __noinline__ void merge_unit_row_wide(const SplitKVParams &p, int u, 
   merge_unit_row<TOut, 8>(p, u, ui, row, c_first, c_last, total, lane, G);
 }
 
+// Barrier over the nt threads that use named barrier 1 (the consumer warps / the softmax group) that also tells
+// every one of them whether all passed true.
+__device__ __forceinline__ bool group_bar_and(bool v, int nt) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)v), "r"(nt)
+      : "memory");
+  return r != 0;
+}
+
+// Plain (untiled) bulk copy global -> shared memory, completion counted in bytes on an mbarrier.  Both addresses
+// 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// Whether merge_unit_bulk can take a unit of R rows cut into nparts parts: either everything fits the buffer at once
+// (parts and gate rows), or at least one part fits beside the gate rows and the running state of every item.
+__device__ __forceinline__ bool merge_bulk_fits(const SplitKVParams &p, int R, int nparts, uint32_t buf_bytes) {
+  const uint32_t block = (uint32_t)(R * PART_STRIDE * sizeof(float));
+  const uint32_t gate = (!p.partial_out && p.do_gate) ? (uint32_t)(R * HEAD_DIM * sizeof(uint16_t)) : 0u;
+  return (uint32_t)nparts * block + gate <= buf_bytes || block + gate + (uint32_t)(R * 64 * 24) <= buf_bytes;
+}
+
+// Merge of one unit's partials by all nt threads of named barrier 1 (the consumer warps of the mma.sync kernel, the
+// softmax group of the tcgen05 kernel) in the CTA that arrived last.
+// A dependent global load costs 0.8 to 2 us at this point of the kernel (the lines were written by other SMs long
+// ago and the pages are cold for this SM), and one warp per row folding part after part is a chain of them:
+// about 10 us for 24 rows x 9 parts, measured, however few the parts.  Here the copy engine fetches the parts
+// instead: the R rows of one part are contiguous in the workspace (R x 1040 bytes), so one bulk copy per part
+// brings everything -- o, m and l -- and the unit's gate rows (per token the six heads of the group are
+// contiguous) into shared memory that is idle by then (buf) in a single round trip, and the fold runs out of
+// shared memory: thread = (row, 4 channels); per wave the maximum first, then a weighted sum in CTA order, so the
+// loads and exponentials of different parts do not depend on one another and the result does not depend on which
+// CTA merges.  A unit with more parts than the buffer holds takes several such waves, the running (acc, m, l) of
+// every item kept in shared memory between them.  The loops are rolled on purpose: this code runs once per CTA,
+// from a cold instruction cache.  Every part c_first .. c_first + nparts - 1 must exist, and merge_bulk_fits()
+// must hold.  Returns false when a wait ran out.
+template <typename TOut>
+__device__ __forceinline__ bool merge_unit_bulk(const SplitKVParams &p, int u, int c_first, int nparts, int t, int nt,
+                                                uint8_t *buf, uint32_t buf_bytes, uint64_t *bar, uint32_t &bar_phase) {
+  const int kvh = u % p.kv_heads, sb = u / p.kv_heads, blk = sb % p.nblk, s = sb / p.nblk;
+  const int tok0 = blk * p.rb, ntok = min(p.rb, p.n_new - tok0);
+  const int R = ntok * GROUP, rs = p.rb * GROUP, n_items = R * 64;
+  const uint32_t block_bytes = (uint32_t)(R * PART_STRIDE * sizeof(float)), bstride = block_bytes / sizeof(float);
+  const uint32_t gate_bytes = (!p.partial_out && p.do_gate) ? (uint32_t)(R * HEAD_DIM * sizeof(uint16_t)) : 0u;
+  const bool single = (uint32_t)nparts * block_bytes + gate_bytes <= buf_bytes;
+  const uint32_t state_bytes = single ? 0u : (uint32_t)(n_items * 24);
+  uint8_t *gbuf = buf + buf_bytes - gate_bytes;                               // gate rows, then the state, at the end
+  float4 *st_acc = reinterpret_cast<float4 *>(gbuf - state_bytes);            // [n_items]
+  float2 *st_ml = reinterpret_cast<float2 *>(gbuf - state_bytes + n_items * 16);  // [n_items]
+  const int per_wave = single ? nparts : (int)((buf_bytes - gate_bytes - state_bytes) / block_bytes);
+  const float *base = p.ws + (size_t)(c_first + u) * rs * PART_STRIDE;  // part k: base + k * rs * PART_STRIDE
+  bool ok = true;
+  for (int k0 = 0; k0 < nparts && ok; k0 += per_wave) {
+    const int n = min(per_wave, nparts - k0);
+    const bool first = k0 == 0, last = k0 + n >= nparts;
+    if (t == 0) {
+      mbar_expect_tx(bar, (uint32_t)n * block_bytes + (first ? gate_bytes : 0u));
+      for (int k = 0; k < n; ++k)
+        bulk_load(buf + (size_t)k * block_bytes, base + (size_t)(k0 + k) * rs * PART_STRIDE, block_bytes, bar);
+      for (int b = 0; b < ntok && first && gate_bytes; ++b)
+        bulk_load(gbuf + (size_t)b * GROUP * HEAD_DIM * sizeof(uint16_t),
+                  p.gate + (((size_t)s * p.n_new + tok0 + b) * p.q_heads + (size_t)kvh * GROUP) * HEAD_DIM,
+                  (uint32_t)(GROUP * HEAD_DIM * sizeof(uint16_t)), bar);
+    }
+    ok = mbar_wait(bar, bar_phase);
+    bar_phase ^= 1u;
+    if (ok) {
+#pragma unroll 1
+      for (int item = t; item < n_items; item += nt) {
+        const int r = item >> 6, c4 = item & 63;
+        const float *rowp = reinterpret_cast<const float *>(buf) + r * PART_STRIDE;
+        float m_prev = -INFINITY, l_run = 0.f;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!first) {
+          a = st_acc[item];
+          const float2 ml = st_ml[item];
+          m_prev = ml.x;
+          l_run = ml.y;
+        }
+        float m_run = m_prev;
+#pragma unroll 4
+        for (int k = 0; k < n; ++k) {
+          const float m = rowp[k * bstride + 256], l = rowp[k * bstride + 257];
+          m_run = fmaxf(m_run, l > 0.f ? m : -INFINITY);
+        }
+        const float sp = (m_prev == -INFINITY) ? 0.f : fast_exp2(m_prev - m_run);
+        l_run *= sp;
+        a.x *= sp; a.y *= sp; a.z *= sp; a.w *= sp;
+#pragma unroll 4
+        for (int k = 0; k < n; ++k) {
+          const float m = rowp[k * bstride + 256], l = rowp[k * bstride + 257];
+          const float4 v = *reinterpret_cast<const float4 *>(rowp + k * bstride + c4 * 4);
+          const float f = l > 0.f ? fast_exp2(m - m_run) : 0.f;
+          l_run = fmaf(l, f, l_run);
+          a.x = fmaf(v.x, f, a.x); a.y = fmaf(v.y, f, a.y); a.z = fmaf(v.z, f, a.z); a.w = fmaf(v.w, f, a.w);
+        }
+        if (!last) {
+          st_acc[item] = a;
+          st_ml[item] = make_float2(m_run, l_run);
+          continue;
+        }
+        const size_t gr = ((size_t)s * p.n_new + tok0 + r / GROUP) * p.q_heads + (size_t)kvh * GROUP + r % GROUP;
+        if (p.partial_out) {
+          float *dst = p.partial_out + gr * PART_STRIDE;
+          *reinterpret_cast<float4 *>(dst + c4 * 4) = a;
+          if (c4 == 0) { dst[256] = m_run; dst[257] = l_run; }
+          continue;
+        }
+        const float inv = __fdividef(1.f, l_run);  // 8 or 16 warps issue this epilogue: the short forms
+        a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
+        if (p.do_gate) {
+          const uint2 g = *reinterpret_cast<const uint2 *>(gbuf + (size_t)r * HEAD_DIM * sizeof(uint16_t) + c4 * 8);
+          a.x *= sigmoid_fast(bf16lo(g.x)); a.y *= sigmoid_fast(bf16hi(g.x));
+          a.z *= sigmoid_fast(bf16lo(g.y)); a.w *= sigmoid_fast(bf16hi(g.y));
+        }
+        if constexpr (sizeof(TOut) == 4) {
+          *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + gr * HEAD_DIM + c4 * 4) = a;
+        } else {
+          *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.out) + gr * HEAD_DIM + c4 * 4) =
+              make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
+        }
+        if (c4 == 0 && p.lse) p.lse[gr] = (m_run + log2f(l_run)) * LN2;
+      }
+    }
+    ok = group_bar_and(ok, nt);  // the buffer is written again by the next wave, or by the next merge
+  }
+  return ok;
+}
+
 // FOLD = false: a dedicated producer warp (warp NCW).  FOLD = true: lane 0 of consumer warp 0 also
 // issues the TMA loads, STAGES - 1 tiles ahead of the tile it is about to consume; the block is then
 // exactly 8 warps and every thread may use up to 255 registers (with a ninth warp the register file
@@ -299,6 +437,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   uint64_t *empty = full + STAGES;
   long long *seg = reinterpret_cast<long long *>(empty + STAGES);  // [0]=total [1]=pre(u_first) [2]=u_first
   volatile int *ticket = reinterpret_cast<volatile int *>(seg + 3);
+  uint64_t *merge_bar = reinterpret_cast<uint64_t *>(seg + 4);  // bulk copies of a merge's parts land on it
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
@@ -306,6 +445,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], NCW); }
+    mbar_init(merge_bar, 1);
     fence_barrier_init();
     prefetch_tensormap(&mapK);
     prefetch_tensormap(&mapV);
@@ -415,6 +555,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     }
   }
 
+  uint32_t merge_phase = 0;
   while (pre < g1 && u < n_units) {
     const UnitInfo ui = unit_info(p, u);
     const int nt_unit = (ui.len + SK_TK - 1) / SK_TK;
@@ -774,6 +915,8 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         grid_dep_wait();  // the append kernel of this step clears the counters
         *ticket = atomicAdd(&p.cnt[u], 1);
         __threadfence();
+        // the parts may be fetched by the copy engine: order its reads after this thread's acquire as well
+        asm volatile("fence.proxy.async;" ::: "memory");
       }
       consumer_sync(NCT);
       const int c_first = cta_of_tile(pre, total, G), c_last = cta_of_tile(pre + nt_unit - 1, total, G);
@@ -785,8 +928,18 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         for (int c = c_first; c <= c_last; ++c) nparts += (total * c / G != total * (c + 1) / G) ? 1 : 0;
       }
       if (*ticket == nparts - 1) {
-        // a unit cut into more than four parts (one sequence alone is cut into dozens) is merged eight parts at a time
-        for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, G);
+        // In the CTA's last segment the K/V ring and the Q region are idle and take the parts by bulk copy (one
+        // sequence alone is cut into dozens of parts: folding them row by row from global memory is a chain of
+        // round trips several times longer than the streaming of its KV).  Earlier segments: the ring already
+        // holds the next segment's tiles, so the parts are folded straight from global memory.
+        constexpr uint32_t MERGE_BUF = (uint32_t)(STAGES * SK_STAGE_BYTES + QREGION);
+        if (pre + nt_unit >= g1 && total >= (long long)G && merge_bulk_fits(p, R, nparts, MERGE_BUF)) {
+          if (!merge_unit_bulk<TOut>(p, u, c_first, nparts, tid, NCT, smem, MERGE_BUF, merge_bar, merge_phase) && tid == 0 &&
+              p.status)
+            *p.status = DEV_ERR_FULL_WAIT;
+        } else {
+          for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, G);
+        }
         if (tid == 0) p.cnt[u] = 0;  // leave the counter clean for a caller that does not reset it
       }
     }

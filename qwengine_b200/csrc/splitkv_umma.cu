@@ -34,7 +34,6 @@ constexpr int DU_MAX_SLOT = 6;             // ring slots when the Q tile is smal
 constexpr int DU_SMEM_TOTAL = 232448 - 1024;   // dynamic shared memory left after the alignment slack
 constexpr int DU_NWG = 4;
 constexpr int DU_MAX_PARTS = 256;         // CTAs of one unit whose liveness is tabulated for the merge
-constexpr int DU_MERGE_BATCH = 10;       // parts of one (row, 4-channel) item fetched together by the block-wide merge
 constexpr int DU_SWITCH_TILES = 8;        // tiles of time charged to a CTA whose slice crosses into the next unit
 constexpr int DU_SM_THREADS = DU_NWG * 128;
 constexpr int DU_CTL_THREADS = 128;        // control warpgroup: TMA producer, MMA issuer, the partition warp, one idle warp
@@ -66,189 +65,6 @@ struct DecCtl {
 // to the K/V ring, where an HBM-bound kernel needs them (bytes in flight = bandwidth x latency).
 __device__ __forceinline__ uint32_t q_tile_off(int row, int d, int sub_bytes) {
   return (uint32_t)((d >> 6) * sub_bytes + row * 128 + ((((d >> 3) & 7) ^ (row & 7)) << 4) + ((d & 7) << 1));
-}
-
-// Barrier over the softmax group (named barrier 1) that also tells every thread whether all of them passed true.
-__device__ __forceinline__ bool softmax_bar_and(bool v) {
-  uint32_t r;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, 1, %2, q;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(r)
-      : "r"((uint32_t)v), "n"(DU_SM_THREADS)
-      : "memory");
-  return r != 0;
-}
-
-// Plain (untiled) bulk copy global -> shared memory, completion counted in bytes on an mbarrier.  Both addresses
-// 16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-
-// Merge of one unit's partials by the whole softmax group (512 threads) of the CTA that arrived last.
-// A dependent global load costs 0.8 to 2 us at this point of the kernel (the lines were written by other SMs long
-// ago and the pages are cold for this SM), and one warp per row folding part after part is a chain of them:
-// about 10 us for 24 rows x 9 parts, measured, however few the parts.  Here the copy engine fetches the parts
-// instead: the R rows of one part are contiguous in the workspace (R x 1040 bytes), so one bulk copy per part
-// brings everything -- o, m and l -- into the idle K/V ring in a single round trip, and the fold runs out of
-// shared memory: thread = (row, 4 channels), parts strictly in CTA order with a running maximum, so the result
-// does not depend on which CTA merges.  Units with more parts than shared memory holds take several such waves.
-// For units of at most 32 rows (four items per thread); every part c_first .. c_first + nparts - 1 exists.
-// Returns false when a wait ran out.
-template <typename TOut>
-__device__ __forceinline__ bool merge_unit_bulk(const SplitKVParams &p, int u, int c_first, int nparts, int t, uint8_t *buf,
-                                                uint32_t buf_bytes, uint64_t *bar, uint32_t &bar_phase,
-                                                volatile int *abort_flag) {
-  const int kvh = u % p.kv_heads, sb = u / p.kv_heads, blk = sb % p.nblk, s = sb / p.nblk;
-  const int tok0 = blk * p.rb, ntok = min(p.rb, p.n_new - tok0);
-  const int R = ntok * GROUP, rs = p.rb * GROUP;
-  const uint32_t block_bytes = (uint32_t)(R * PART_STRIDE * sizeof(float));
-  const int per_wave = (int)(buf_bytes / block_bytes);
-  const float *base = p.ws + (size_t)(c_first + u) * rs * PART_STRIDE;  // part k: base + k * rs * PART_STRIDE
-  const uint32_t gate_bytes = (!p.partial_out && p.do_gate) ? (uint32_t)(R * HEAD_DIM * sizeof(uint16_t)) : 0u;
-  if ((uint32_t)nparts * block_bytes + gate_bytes <= buf_bytes) {
-    // Everything fits at once (the usual case: up to 8 parts of 24 rows): one round trip brings the parts and the
-    // unit's gate rows (per token the six heads of the group are contiguous), and the rest runs out of shared
-    // memory in two rolled loops -- this code runs once per CTA, from a cold instruction cache, so it is kept short.
-    uint8_t *gbuf = buf + (size_t)nparts * block_bytes;
-    if (t == 0) {
-      mbar_expect_tx(bar, (uint32_t)nparts * block_bytes + gate_bytes);
-      for (int k = 0; k < nparts; ++k)
-        bulk_load(buf + (size_t)k * block_bytes, base + (size_t)k * rs * PART_STRIDE, block_bytes, bar);
-      for (int b = 0; b < ntok && gate_bytes; ++b)
-        bulk_load(gbuf + (size_t)b * GROUP * HEAD_DIM * sizeof(uint16_t),
-                  p.gate + (((size_t)s * p.n_new + tok0 + b) * p.q_heads + (size_t)kvh * GROUP) * HEAD_DIM,
-                  (uint32_t)(GROUP * HEAD_DIM * sizeof(uint16_t)), bar);
-    }
-    bool ok1 = wait_or_abort(bar, bar_phase, abort_flag);
-    bar_phase ^= 1u;
-    if (ok1) {
-#pragma unroll 1
-      for (int item = t; item < R * 64; item += DU_SM_THREADS) {
-        const int r = item >> 6, c4 = item & 63;
-        const float *rowp = reinterpret_cast<const float *>(buf) + r * PART_STRIDE;
-        // maximum first, then a weighted sum in CTA order: the loads and exponentials of different parts do not
-        // depend on one another, only the additions chain
-        const uint32_t bstride = block_bytes / sizeof(float);
-        float m_run = -INFINITY, l_run = 0.f;
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int k = 0; k < nparts; ++k) {
-          const float m = rowp[k * bstride + 256], l = rowp[k * bstride + 257];
-          m_run = fmaxf(m_run, l > 0.f ? m : -INFINITY);
-        }
-#pragma unroll 4
-        for (int k = 0; k < nparts; ++k) {
-          const float m = rowp[k * bstride + 256], l = rowp[k * bstride + 257];
-          const float4 v = *reinterpret_cast<const float4 *>(rowp + k * bstride + c4 * 4);
-          const float f = l > 0.f ? fast_exp2(m - m_run) : 0.f;
-          l_run = fmaf(l, f, l_run);
-          a.x = fmaf(v.x, f, a.x); a.y = fmaf(v.y, f, a.y); a.z = fmaf(v.z, f, a.z); a.w = fmaf(v.w, f, a.w);
-        }
-        const size_t gr = ((size_t)s * p.n_new + tok0 + r / GROUP) * p.q_heads + (size_t)kvh * GROUP + r % GROUP;
-        if (p.partial_out) {
-          float *dst = p.partial_out + gr * PART_STRIDE;
-          *reinterpret_cast<float4 *>(dst + c4 * 4) = a;
-          if (c4 == 0) { dst[256] = m_run; dst[257] = l_run; }
-          continue;
-        }
-        const float inv = __fdividef(1.f, l_run);  // as the kernel's own final store does: 16 warps issue this epilogue
-        a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
-        if (p.do_gate) {
-          const uint2 g = *reinterpret_cast<const uint2 *>(gbuf + (size_t)r * HEAD_DIM * sizeof(uint16_t) + c4 * 8);
-          a.x *= sigmoid_fast(bf16lo(g.x)); a.y *= sigmoid_fast(bf16hi(g.x));
-          a.z *= sigmoid_fast(bf16lo(g.y)); a.w *= sigmoid_fast(bf16hi(g.y));
-        }
-        if constexpr (sizeof(TOut) == 4) {
-          *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + gr * HEAD_DIM + c4 * 4) = a;
-        } else {
-          *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.out) + gr * HEAD_DIM + c4 * 4) =
-              make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
-        }
-        if (c4 == 0 && p.lse) p.lse[gr] = (m_run + log2f(l_run)) * LN2;
-      }
-    }
-    return softmax_bar_and(ok1);  // the buffer is written again by the next merge
-  }
-  size_t grow[4];
-  uint2 g2[4];
-  float4 acc[4];
-  float mg[4], lg[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int item = t + i * DU_SM_THREADS, r = item >> 6, c4 = item & 63;
-    grow[i] = ((size_t)s * p.n_new + tok0 + r / GROUP) * p.q_heads + (size_t)kvh * GROUP + r % GROUP;
-    g2[i] = make_uint2(0, 0);
-    if (item < R * 64 && !p.partial_out && p.do_gate)  // in flight together with the first wave of parts
-      g2[i] = *reinterpret_cast<const uint2 *>(p.gate + grow[i] * HEAD_DIM + c4 * 4);
-    acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    mg[i] = -INFINITY;
-    lg[i] = 0.f;
-  }
-  bool ok = true;
-  for (int k0 = 0; k0 < nparts && ok; k0 += per_wave) {
-    const int n = min(per_wave, nparts - k0);
-    if (t == 0) {
-      mbar_expect_tx(bar, (uint32_t)n * block_bytes);
-      for (int k = 0; k < n; ++k)
-        bulk_load(buf + (size_t)k * block_bytes, base + (size_t)(k0 + k) * rs * PART_STRIDE, block_bytes, bar);
-    }
-    ok = wait_or_abort(bar, bar_phase, abort_flag);
-    bar_phase ^= 1u;
-    if (ok) {
-      for (int k = 0; k < n; ++k) {
-        const float *part = reinterpret_cast<const float *>(buf + (size_t)k * block_bytes);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int item = t + i * DU_SM_THREADS, r = item >> 6, c4 = item & 63;
-          if (item >= R * 64) continue;
-          const float *rowp = part + r * PART_STRIDE;
-          const float m = rowp[256], l = rowp[257];
-          if (!(l > 0.f)) continue;
-          const float4 v = *reinterpret_cast<const float4 *>(rowp + c4 * 4);
-          const float m_new = fmaxf(mg[i], m);
-          const float f_old = fast_exp2(mg[i] - m_new), f = fast_exp2(m - m_new);  // mg = -inf gives f_old = 0
-          mg[i] = m_new;
-          lg[i] = lg[i] * f_old + l * f;
-          acc[i].x = acc[i].x * f_old + v.x * f; acc[i].y = acc[i].y * f_old + v.y * f;
-          acc[i].z = acc[i].z * f_old + v.z * f; acc[i].w = acc[i].w * f_old + v.w * f;
-        }
-      }
-    }
-    // the buffer is written again by the next wave, or by the next merge
-    ok = softmax_bar_and(ok);
-  }
-  if (!ok) return false;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int item = t + i * DU_SM_THREADS, c4 = item & 63;
-    if (item >= R * 64) continue;
-    if (p.partial_out) {
-      float *dst = p.partial_out + grow[i] * PART_STRIDE;
-      *reinterpret_cast<float4 *>(dst + c4 * 4) = acc[i];
-      if (c4 == 0) { dst[256] = mg[i]; dst[257] = lg[i]; }
-      continue;
-    }
-    const float inv = 1.f / lg[i];
-    float4 o = make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv);
-    if (p.do_gate) {
-      o.x *= sigmoidf_(bf16lo(g2[i].x)); o.y *= sigmoidf_(bf16hi(g2[i].x));
-      o.z *= sigmoidf_(bf16lo(g2[i].y)); o.w *= sigmoidf_(bf16hi(g2[i].y));
-    }
-    if constexpr (sizeof(TOut) == 4) {
-      *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + grow[i] * HEAD_DIM + c4 * 4) = o;
-    } else {
-      *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.out) + grow[i] * HEAD_DIM + c4 * 4) =
-          make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
-    }
-    if (c4 == 0 && p.lse) p.lse[grow[i]] = (mg[i] + log2f(lg[i])) * LN2;
-  }
-  return true;
 }
 
 template <typename TOut>
@@ -801,11 +617,11 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           const int c_first = pend_cf[k], c_last = pend_cl[k];
           const int blk = (pend_u[k] / p.kv_heads) % p.nblk;  // no load on the way to the merge: unit_info reads pos
           const int R = min(p.rb, p.n_new - blk * p.rb) * GROUP, span = c_last - c_first + 1;
-          if (all_live && R <= 32) {
-            // the Q tile and the K/V ring are idle by now: one buffer from the start of Q to the control block
-            if (!merge_unit_bulk<TOut>(p, pend_u[k], c_first, span, st_tid, q_smem,
-                                       (uint32_t)(reinterpret_cast<uint8_t *>(ctl) - q_smem) & ~15u,
-                                       &ctl->merge_bar, merge_phase, abort_flag)) {
+          // the Q tile and the K/V ring are idle by now: one buffer from the start of Q to the control block
+          const uint32_t buf_bytes = (uint32_t)(reinterpret_cast<uint8_t *>(ctl) - q_smem) & ~15u;
+          if (all_live && merge_bulk_fits(p, R, span, buf_bytes)) {
+            if (!merge_unit_bulk<TOut>(p, pend_u[k], c_first, span, st_tid, DU_SM_THREADS, q_smem, buf_bytes,
+                                       &ctl->merge_bar, merge_phase)) {
               if (st_tid == 0) fail(DEV_ERR_SOFTMAX_WAIT);
               break;
             }
