@@ -312,13 +312,16 @@ __device__ __forceinline__ bool merge_bulk_fits(const SplitKVParams &p, int R, i
 // contiguous) into shared memory that is idle by then (buf) in a single round trip, and the fold runs out of
 // shared memory: thread = (row, 4 channels); per wave the maximum first, then a weighted sum in CTA order, so the
 // loads and exponentials of different parts do not depend on one another and the result does not depend on which
-// CTA merges.  A unit with more parts than the buffer holds takes several such waves, the running (acc, m, l) of
-// every item kept in shared memory between them.  The loops are rolled on purpose: this code runs once per CTA,
-// from a cold instruction cache.  Every part c_first .. c_first + nparts - 1 must exist, and merge_bulk_fits()
-// must hold.  Returns false when a wait ran out.
+// CTA merges.  A unit with more parts than the buffer holds (one sequence alone is cut into 37) takes several such
+// waves, the running (acc, m, l) of every item kept in shared memory between them; the parts area is then used as
+// two halves, so that the copy engine fetches the next wave while this one is folded and only the first round trip
+// is exposed.  The loops are rolled on purpose: this code runs once per CTA, from a cold instruction cache.
+// Every part c_first .. c_first + nparts - 1 must exist, and merge_bulk_fits() must hold.  bars: two mbarriers
+// (one arrival each); phases: bit i = parity that the next wave on bars[i] completes.  Returns false when a wait
+// ran out.
 template <typename TOut>
 __device__ __forceinline__ bool merge_unit_bulk(const SplitKVParams &p, int u, int c_first, int nparts, int t, int nt,
-                                                uint8_t *buf, uint32_t buf_bytes, uint64_t *bar, uint32_t &bar_phase) {
+                                                uint8_t *buf, uint32_t buf_bytes, uint64_t *bars, uint32_t &phases) {
   const int kvh = u % p.kv_heads, sb = u / p.kv_heads, blk = sb % p.nblk, s = sb / p.nblk;
   const int tok0 = blk * p.rb, ntok = min(p.rb, p.n_new - tok0);
   const int R = ntok * GROUP, rs = p.rb * GROUP, n_items = R * 64;
@@ -329,28 +332,40 @@ __device__ __forceinline__ bool merge_unit_bulk(const SplitKVParams &p, int u, i
   uint8_t *gbuf = buf + buf_bytes - gate_bytes;                               // gate rows, then the state, at the end
   float4 *st_acc = reinterpret_cast<float4 *>(gbuf - state_bytes);            // [n_items]
   float2 *st_ml = reinterpret_cast<float2 *>(gbuf - state_bytes + n_items * 16);  // [n_items]
-  const int per_wave = single ? nparts : (int)((buf_bytes - gate_bytes - state_bytes) / block_bytes);
+  // parts per wave: all of them, or what half of the parts area holds (one at least: the halves then overlap
+  // and the waves simply follow one another)
+  const uint32_t area = buf_bytes - gate_bytes - state_bytes;
+  const int half_cap = (int)(area / 2 / block_bytes);
+  const int per_wave = single ? nparts : max(half_cap, 1);
+  const uint32_t half_off = half_cap >= 1 ? (uint32_t)half_cap * block_bytes : 0u;
   const float *base = p.ws + (size_t)(c_first + u) * rs * PART_STRIDE;  // part k: base + k * rs * PART_STRIDE
+  auto issue = [&](int w) {  // thread 0: the copies of wave w, into half w & 1, counted on bars[w & 1]
+    const int k0 = w * per_wave, n = min(per_wave, nparts - k0);
+    uint64_t *bar = bars + (w & 1);
+    uint8_t *dst = buf + (w & 1) * half_off;
+    mbar_expect_tx(bar, (uint32_t)n * block_bytes + (w == 0 ? gate_bytes : 0u));
+    for (int k = 0; k < n; ++k)
+      bulk_load(dst + (size_t)k * block_bytes, base + (size_t)(k0 + k) * rs * PART_STRIDE, block_bytes, bar);
+    for (int b = 0; b < ntok && w == 0 && gate_bytes; ++b)
+      bulk_load(gbuf + (size_t)b * GROUP * HEAD_DIM * sizeof(uint16_t),
+                p.gate + (((size_t)s * p.n_new + tok0 + b) * p.q_heads + (size_t)kvh * GROUP) * HEAD_DIM,
+                (uint32_t)(GROUP * HEAD_DIM * sizeof(uint16_t)), bar);
+  };
+  const int n_waves = (nparts + per_wave - 1) / per_wave;
+  const bool overlap = half_cap >= 1;  // the next wave may be fetched while this one is folded
   bool ok = true;
-  for (int k0 = 0; k0 < nparts && ok; k0 += per_wave) {
-    const int n = min(per_wave, nparts - k0);
-    const bool first = k0 == 0, last = k0 + n >= nparts;
-    if (t == 0) {
-      mbar_expect_tx(bar, (uint32_t)n * block_bytes + (first ? gate_bytes : 0u));
-      for (int k = 0; k < n; ++k)
-        bulk_load(buf + (size_t)k * block_bytes, base + (size_t)(k0 + k) * rs * PART_STRIDE, block_bytes, bar);
-      for (int b = 0; b < ntok && first && gate_bytes; ++b)
-        bulk_load(gbuf + (size_t)b * GROUP * HEAD_DIM * sizeof(uint16_t),
-                  p.gate + (((size_t)s * p.n_new + tok0 + b) * p.q_heads + (size_t)kvh * GROUP) * HEAD_DIM,
-                  (uint32_t)(GROUP * HEAD_DIM * sizeof(uint16_t)), bar);
-    }
-    ok = mbar_wait(bar, bar_phase);
-    bar_phase ^= 1u;
+  if (t == 0) issue(0);
+  for (int w = 0; w < n_waves && ok; ++w) {
+    const int k0 = w * per_wave, n = min(per_wave, nparts - k0);
+    const bool first = w == 0, last = w == n_waves - 1;
+    if (t == 0 && overlap && !last) issue(w + 1);
+    ok = mbar_wait(bars + (w & 1), (phases >> (w & 1)) & 1u);
+    phases ^= 1u << (w & 1);
     if (ok) {
 #pragma unroll 1
       for (int item = t; item < n_items; item += nt) {
         const int r = item >> 6, c4 = item & 63;
-        const float *rowp = reinterpret_cast<const float *>(buf) + r * PART_STRIDE;
+        const float *rowp = reinterpret_cast<const float *>(buf + (w & 1) * half_off) + r * PART_STRIDE;
         float m_prev = -INFINITY, l_run = 0.f;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
         if (!first) {
@@ -404,7 +419,8 @@ __device__ __forceinline__ bool merge_unit_bulk(const SplitKVParams &p, int u, i
         if (c4 == 0 && p.lse) p.lse[gr] = (m_run + log2f(l_run)) * LN2;
       }
     }
-    ok = group_bar_and(ok, nt);  // the buffer is written again by the next wave, or by the next merge
+    ok = group_bar_and(ok, nt);  // this half is written again by the wave after the next, or by the next merge
+    if (t == 0 && ok && !overlap && !last) issue(w + 1);
   }
   return ok;
 }
@@ -437,7 +453,8 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   uint64_t *empty = full + STAGES;
   long long *seg = reinterpret_cast<long long *>(empty + STAGES);  // [0]=total [1]=pre(u_first) [2]=u_first
   volatile int *ticket = reinterpret_cast<volatile int *>(seg + 3);
-  uint64_t *merge_bar = reinterpret_cast<uint64_t *>(seg + 4);  // bulk copies of a merge's parts land on it
+  uint64_t *merge_bar = reinterpret_cast<uint64_t *>(seg + 4);  // two: bulk copies of a merge's parts land on them
+  volatile int *pend = reinterpret_cast<volatile int *>(seg + 6);  // units this CTA is to merge, and [8] their count
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
@@ -446,6 +463,8 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], NCW); }
     mbar_init(merge_bar, 1);
+    mbar_init(merge_bar + 1, 1);
+    pend[8] = 0;
     fence_barrier_init();
     prefetch_tensormap(&mapK);
     prefetch_tensormap(&mapV);
@@ -555,7 +574,6 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     }
   }
 
-  uint32_t merge_phase = 0;
   while (pre < g1 && u < n_units) {
     const UnitInfo ui = unit_info(p, u);
     const int nt_unit = (ui.len + SK_TK - 1) / SK_TK;
@@ -904,7 +922,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         if (c8 == 0) { dst[256] = mg; dst[257] = lg; }
       }
     }
-    // ---- with arrival counters: the CTA that completes a unit last merges it right here ----
+    // ---- with arrival counters: the CTA that completes a unit last merges it (after its own last tile) ----
     if (!whole && p.cnt) {
       // Release: the barrier orders every thread's partial stores before thread 0's fence, which is cumulative,
       // so one fence + atomic publishes the whole CTA's partial.  Acquire: the fence after the atomic, then the
@@ -927,24 +945,37 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         nparts = 0;
         for (int c = c_first; c <= c_last; ++c) nparts += (total * c / G != total * (c + 1) / G) ? 1 : 0;
       }
-      if (*ticket == nparts - 1) {
-        // In the CTA's last segment the K/V ring and the Q region are idle and take the parts by bulk copy (one
-        // sequence alone is cut into dozens of parts: folding them row by row from global memory is a chain of
-        // round trips several times longer than the streaming of its KV).  Earlier segments: the ring already
-        // holds the next segment's tiles, so the parts are folded straight from global memory.
-        constexpr uint32_t MERGE_BUF = (uint32_t)(STAGES * SK_STAGE_BYTES + QREGION);
-        if (pre + nt_unit >= g1 && total >= (long long)G && merge_bulk_fits(p, R, nparts, MERGE_BUF)) {
-          if (!merge_unit_bulk<TOut>(p, u, c_first, nparts, tid, NCT, smem, MERGE_BUF, merge_bar, merge_phase) && tid == 0 &&
-              p.status)
-            *p.status = DEV_ERR_FULL_WAIT;
-        } else {
-          for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, u, ui, row, c_first, c_last, total, lane, G);
-        }
-        if (tid == 0) p.cnt[u] = 0;  // leave the counter clean for a caller that does not reset it
+      // The merge itself waits until this CTA has no tiles left: the K/V ring is idle then and takes the parts by
+      // bulk copy (one sequence alone is cut into dozens of parts: folding them row by row from global memory is
+      // a chain of round trips several times longer than the streaming of its KV).  Which way a unit is merged
+      // must not depend on which CTA happens to arrive last -- the two ways round differently -- and with the
+      // merge deferred it depends on the shapes alone.  A slice has at most two cut units: its first and its last.
+      // The notes -- (unit, first CTA, last CTA, parts) each and their count -- live in shared memory: the tile
+      // loop has no register to spare for them.
+      if (tid == 0 && *ticket == nparts - 1 && pend[8] < 2) {
+        const int n = pend[8];
+        pend[4 * n] = u; pend[4 * n + 1] = c_first; pend[4 * n + 2] = c_last; pend[4 * n + 3] = nparts;
+        pend[8] = n + 1;
       }
     }
     pre += nt_unit;
     ++u;
+  }
+  consumer_sync(NCT);  // thread 0's notes above
+  const int n_pend = pend[8];
+  uint32_t merge_phase = 0;
+  for (int k = 0; k < n_pend; ++k) {
+    constexpr uint32_t MERGE_BUF = (uint32_t)(STAGES * SK_STAGE_BYTES + QREGION);
+    const int um = pend[4 * k], cf = pend[4 * k + 1], cl = pend[4 * k + 2], np = pend[4 * k + 3];
+    const int R = min(p.rb, p.n_new - ((um / p.kv_heads) % p.nblk) * p.rb) * GROUP;
+    if (total >= (long long)G && merge_bulk_fits(p, R, np, MERGE_BUF)) {
+      if (!merge_unit_bulk<TOut>(p, um, cf, np, tid, NCT, smem, MERGE_BUF, merge_bar, merge_phase) && tid == 0 && p.status)
+        *p.status = DEV_ERR_FULL_WAIT;
+    } else {
+      const UnitInfo ui = unit_info(p, um);
+      for (int row = warp; row < R; row += NCW) merge_unit_row<TOut>(p, um, ui, row, cf, cl, total, lane, G);
+    }
+    if (tid == 0) p.cnt[um] = 0;  // leave the counter clean for a caller that does not reset it
   }
 }
 
@@ -1090,7 +1121,7 @@ __global__ void __launch_bounds__(256) combine_partials_peer_kernel(const float 
 template <int MT, int DS, int STAGES>
 constexpr size_t splitkv_smem_bytes() {
   return 1024 + (size_t)STAGES * SK_STAGE_BYTES + (size_t)MT * 16 * 1024 + 2 * SK_KS * MT * 16 * 4 +
-         2 * STAGES * 8 + 3 * 8 + 64;
+         2 * STAGES * 8 + 3 * 8 + 96;
 }
 
 }  // namespace qwb

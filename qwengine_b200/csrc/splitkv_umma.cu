@@ -43,7 +43,7 @@ constexpr int DU_CTL_REGS = 64, DU_SM_REGS = 104;  // after setmaxnreg: 128 x 64
 struct DecCtl {
   uint64_t q_ready, o_free, s_full[2], p_full[2], o_done[2];
   uint64_t slot_full[DU_MAX_SLOT], slot_empty[DU_MAX_SLOT];
-  uint64_t merge_bar;            // bulk copies of a merge's parts land on it
+  uint64_t merge_bar[2];         // bulk copies of a merge's parts land on them
   uint32_t tmem_base;
   volatile int abort_flag;
   volatile int ticket[2];
@@ -94,7 +94,8 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       mbar_init(&ctl->o_done[i], 1);
     }
     for (int i = 0; i < DU_MAX_SLOT; ++i) { mbar_init(&ctl->slot_full[i], 1); mbar_init(&ctl->slot_empty[i], 1); }
-    mbar_init(&ctl->merge_bar, 1);
+    mbar_init(&ctl->merge_bar[0], 1);
+    mbar_init(&ctl->merge_bar[1], 1);
     ctl->abort_flag = (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) ? 1 : 0;
     fence_barrier_init();
     prefetch_tensormap(&mapK);
@@ -621,7 +622,7 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
           const uint32_t buf_bytes = (uint32_t)(reinterpret_cast<uint8_t *>(ctl) - q_smem) & ~15u;
           if (all_live && merge_bulk_fits(p, R, span, buf_bytes)) {
             if (!merge_unit_bulk<TOut>(p, pend_u[k], c_first, span, st_tid, DU_SM_THREADS, q_smem, buf_bytes,
-                                       &ctl->merge_bar, merge_phase)) {
+                                       ctl->merge_bar, merge_phase)) {
               if (st_tid == 0) fail(DEV_ERR_SOFTMAX_WAIT);
               break;
             }
