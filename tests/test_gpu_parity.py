@@ -107,6 +107,16 @@ def test_config2_shape_reduced():
     _full_check(Case(40, [2048] * 16, 1), "config2-reduced")
 
 
+@pytest.mark.parametrize("n_seq,hist", [(13, 333), (18, 1), (16, 1000)])
+def test_uniform_batches_that_give_every_unit_two_ctas(n_seq, hist):
+    """50 to 74 equally long units on 148 SMs: the grid is trimmed to two CTAs per unit (one-tile units leave every
+    other CTA without work).  Checked against the oracle and for run-to-run identity."""
+    c = Case(43 + n_seq, [hist] * n_seq, 1)
+    _full_check(c, "uniform %d x %d" % (n_seq, hist))
+    a, b = run_case(c), run_case(c)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
 def test_config3_shape_reduced():
     """BASELINE config 3 shape: 8 sequences x 4 draft tokens, ragged histories."""
     rng = np.random.default_rng(41)
