@@ -149,3 +149,33 @@ def test_mixed_serving_step_partitioned_by_kv_bytes():
     assert np.array_equal(host_bits(kcp), kc_ref)
     check_out(host_f32(o).reshape(-1, 24, 256)[rows], ref, "prefill chunks of the mixed step")
     check_lse(l.cpu().numpy().reshape(-1, 24)[rows], lse_ref, "prefill chunks of the mixed step")
+
+
+@pytest.mark.parametrize("hist,CH", [(0, 256), (700, 512)])
+def test_query_rows_of_a_chunk_split_zigzag_between_two_shares(hist, CH):
+    """The 8-GPU plan of the long prefill: two GPUs share a KV head, both append the whole chunk (rope(k) + store,
+    no attention) and each attends for its query-row blocks only -- rows [0, CH/4) and [3CH/4, CH) on one,
+    [CH/4, 3CH/4) on the other -- with the position set to the block's first row and nothing appended.  Run here one
+    share after the other on one GPU; every row must match the oracle, the cache must be the chunk call's cache."""
+    c = Case(520 + CH, [hist], CH, kv_heads=1)
+    ref, lse_ref, kc_ref, vc_ref = c.oracle()
+    q, gate = dev_bf16(c.q), dev_bf16(c.gate)
+    out = torch.zeros(1, CH, 6, 256, dtype=torch.float32, device="cuda")
+    lse = torch.zeros(1, CH, 6, dtype=torch.float32, device="cuda")
+    for blocks in ([(0, CH // 4), (3 * CH // 4, CH // 4)], [(CH // 4, CH // 2)]):
+        kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)   # each share holds its own copy of the cache
+        ma = api.Mixer(1, CH, kv_heads=1)
+        ma.bind_append_only(kc, vc, torch.tensor([hist], dtype=torch.int32, device="cuda"), dev_bf16(c.k), dev_bf16(c.v))
+        ma.forward()
+        for off, n in blocks:
+            mx = api.Mixer(1, n, kv_heads=1)
+            sl = slice(off, off + n)
+            mx.bind(q[:, sl].contiguous(), kc, vc, torch.tensor([hist + off], dtype=torch.int32, device="cuda"),
+                    out[:, sl], gate=gate[:, sl].contiguous(), lse=lse[:, sl], flags=api.F_ROPE | api.F_GATE)
+            mx.forward()
+            torch.cuda.synchronize()
+            mx.check_status()
+        ma.check_status()
+        assert np.array_equal(host_bits(kc), kc_ref) and np.array_equal(host_bits(vc), vc_ref)
+    check_out(host_f32(out), ref, "zig-zag row split")
+    check_lse(lse.cpu().numpy(), lse_ref, "zig-zag row split")
