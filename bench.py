@@ -687,15 +687,21 @@ def measure_mixed(args, rank, world, peaks, ex_cls):
                                 cache_row=torch.tensor([t[1] for t in tails], dtype=torch.int64, device="cuda"),
                                 q_pos=q_pos[[t[0] for t in tails]].contiguous())
 
-        def split_step():
+        # This rank's partials are published FIRST and merged LAST, with the whole sequences' call in between: by the
+        # time a rank reads its peers' partials they have long been written, so the combine does not wait for the
+        # slowest rank (merged right after publishing it took 31 us at 2 GPUs and 76 us at 4, nearly all of it waiting).
+        def split_publish():
             if ma is not None:
                 ma.forward()
             part = ex.partial()
             part.zero_()                              # ranks without a range of a sequence contribute l = 0
             mp.forward_partial(part)
+
+        def split_combine():
             ex.combine(out_s, gate=gs.view(n_split, 24, 256))
 
-        calls.append(split_step)
+        calls.insert(0, split_publish)
+        calls.append(split_combine)
     # -- prefill chunks: 2 x 4096 tokens; chunk and KV heads by rank
     per_chunk = max(1, world // 2)
     kvh_p = 4 // per_chunk if world > 1 else 4
@@ -715,18 +721,18 @@ def measure_mixed(args, rank, world, peaks, ex_cls):
     ms_dec = timed(decode_part, steps, 3, args.repeats, world)
     ms_pre = timed(mpf.forward, steps, 3, args.repeats, world)
     ms_all = timed(whole_step, steps, 3, args.repeats, world)
-    comb_ms = None
-    if ex is not None:   # the combine's share: an event pair around it alone
+    comb_ms = comb_ms_last = None
+    if ex is not None:   # the combine's share: an event pair around it, in its place at the end of the step
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t = []
         for _ in range(5):
-            if ma is not None:
-                ma.forward()
-            part = ex.partial(); part.zero_(); mp.forward_partial(part)
-            e0.record(); ex.combine(out_s, gate=gs.view(n_split, 24, 256)); e1.record()
+            for c in calls[:-1]:
+                c()
+            e0.record(); calls[-1](); e1.record()
             torch.cuda.synchronize()
             t.append(e0.elapsed_time(e1))
         comb_ms = rank_max([float(np.median(t))], world)[0]
+        comb_ms_last = -rank_max([-float(np.median(t))], world)[0]   # the rank that arrives last waits for nobody
         ex.check_status()
     kv_total = float(lens.sum()) * KV_BYTES_PER_TOKEN
     flops_total = 2 * float(4096 * 4097 // 2) * FLOPS_PER_PAIR
@@ -738,8 +744,10 @@ def measure_mixed(args, rank, world, peaks, ex_cls):
             "scaling": "strong", "n_gpus": world,
             "decode_part": {"value": round(kv_total / (d * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(d, 5),
                             "ms_per_step_stats": stats(ms_dec), "hbm_frac_of_step": round(kv_total / (d * 1e-3) / 1e9 / (peaks[0] * world), 4),
-                            "includes": "append, attention, partial exchange and combine"},
+                            "includes": "append, attention, partial exchange and combine (partials published first, merged last)"},
             "combine_ms": None if comb_ms is None else round(comb_ms, 5),
+            "combine_ms_what": "max over ranks: a rank that reaches its combine early waits there for the slowest rank's flag",
+            "combine_ms_of_the_last_rank": None if comb_ms is None else round(comb_ms_last, 5),
             "combine_share_of_decode_part": None if comb_ms is None else round(comb_ms / d, 4),
             "nvlink_bytes_read_per_rank_per_step": 0 if ex is None else n_split * 24 * 260 * 4 * (world - 1),
             "prefill_part": {"value": round(flops_total / (pf * 1e-3) / 1e12, 1), "unit": "TFLOP/s", "ms_per_step": round(pf, 5)},

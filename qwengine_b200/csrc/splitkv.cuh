@@ -1064,19 +1064,21 @@ __global__ void __launch_bounds__(256) combine_partials_peer_kernel(const float 
   if (threadIdx.x == 0) {
     failed = 0;
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag_ptrs[rank]), "r"(step) : "memory");
+  }
+  __syncthreads();
+  // one thread per peer: the polls (a round trip over NVLink each) run side by side, not one peer after the other
+  for (int k = threadIdx.x; k < n_parts; k += blockDim.x) {
+    if (k == rank) continue;
+    const int *f = flag_ptrs[k];
     const uint64_t t0 = global_timer_ns();
-    for (int k = 0; k < n_parts && !failed; ++k) {
-      if (k == rank) continue;
-      const int *f = flag_ptrs[k];
-      for (;;) {
-        int v;
-        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-        if (v - step >= 0) break;  // the peer is at this step (or already past it)
-        if (global_timer_ns() - t0 > PEER_WAIT_NS) {
-          failed = 1;
-          if (status) *status = DEV_ERR_PEER_WAIT;
-          break;
-        }
+    for (;;) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (v - step >= 0) break;  // the peer is at this step (or already past it)
+      if (global_timer_ns() - t0 > PEER_WAIT_NS) {
+        failed = 1;
+        if (status) *status = DEV_ERR_PEER_WAIT;
+        break;
       }
     }
   }
@@ -1085,24 +1087,53 @@ __global__ void __launch_bounds__(256) combine_partials_peer_kernel(const float 
   const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (r >= n) return;
-  float mg = -INFINITY;
-  for (int k = 0; k < n_parts; ++k) {
-    const float *src = part_ptrs[k] + (size_t)r * PART_STRIDE;
-    if (src[257] > 0.f) mg = fmaxf(mg, src[256]);
-  }
-  const float m_use = (mg == -INFINITY) ? 0.f : mg;
+  // A load from a peer's memory is a round trip over NVLink (2 to 3 us); chained one after the other -- the test of
+  // l, then m, then the row, per part -- they made this kernel 31 us at two ranks and 76 us at four.  All loads of up
+  // to eight parts are issued together, then folded in rank order with the arithmetic of combine_partials_kernel.
+  float mg = -INFINITY, lg = 0.f;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  float lg = 0.f;
-  for (int k = 0; k < n_parts; ++k) {  // rank order, as in combine_partials_kernel: same bits
-    const float *src = part_ptrs[k] + (size_t)r * PART_STRIDE;
-    const float l = src[257];
-    if (!(l > 0.f)) continue;
-    const float f = fast_exp2(src[256] - m_use);
-    lg += l * f;
-    const float4 a = *reinterpret_cast<const float4 *>(src + lane * 8);
-    const float4 b = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
-    acc[0] += a.x * f; acc[1] += a.y * f; acc[2] += a.z * f; acc[3] += a.w * f;
-    acc[4] += b.x * f; acc[5] += b.y * f; acc[6] += b.z * f; acc[7] += b.w * f;
+  if (n_parts <= 8) {
+    float mv[8], lv[8];
+    float4 av[8], bv[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k < n_parts) {
+        const float *src = part_ptrs[k] + (size_t)r * PART_STRIDE;
+        mv[k] = src[256];
+        lv[k] = src[257];
+        av[k] = *reinterpret_cast<const float4 *>(src + lane * 8);
+        bv[k] = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < n_parts && lv[k] > 0.f) mg = fmaxf(mg, mv[k]);
+    const float m_use = (mg == -INFINITY) ? 0.f : mg;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k >= n_parts || !(lv[k] > 0.f)) continue;
+      const float f = fast_exp2(mv[k] - m_use);
+      lg += lv[k] * f;
+      acc[0] += av[k].x * f; acc[1] += av[k].y * f; acc[2] += av[k].z * f; acc[3] += av[k].w * f;
+      acc[4] += bv[k].x * f; acc[5] += bv[k].y * f; acc[6] += bv[k].z * f; acc[7] += bv[k].w * f;
+    }
+  } else {
+    for (int k = 0; k < n_parts; ++k) {
+      const float *src = part_ptrs[k] + (size_t)r * PART_STRIDE;
+      if (src[257] > 0.f) mg = fmaxf(mg, src[256]);
+    }
+    const float m_use = (mg == -INFINITY) ? 0.f : mg;
+    for (int k = 0; k < n_parts; ++k) {  // rank order, as in combine_partials_kernel: same bits
+      const float *src = part_ptrs[k] + (size_t)r * PART_STRIDE;
+      const float l = src[257];
+      if (!(l > 0.f)) continue;
+      const float f = fast_exp2(src[256] - m_use);
+      lg += l * f;
+      const float4 a4 = *reinterpret_cast<const float4 *>(src + lane * 8);
+      const float4 b4 = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
+      acc[0] += a4.x * f; acc[1] += a4.y * f; acc[2] += a4.z * f; acc[3] += a4.w * f;
+      acc[4] += b4.x * f; acc[5] += b4.y * f; acc[6] += b4.z * f; acc[7] += b4.w * f;
+    }
   }
   const float inv = 1.f / lg;
   if (gate) {
