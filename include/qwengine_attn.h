@@ -23,6 +23,15 @@
  * Geometry supported: head_dim 256, rotary_dim 64, q_heads = 6 * kv_heads,
  * kv_heads in {1, 2, 4} (4 is the model; 1 and 2 are the per-GPU slices of a
  * KV-head-sharded layer).  Anything else returns QW_ERR_SHAPE.
+ *
+ * Programmatic dependent launch.  The fused calls (qw_mixer_forward*) launch their
+ * first kernel with cudaLaunchAttributeProgrammaticStreamSerialization; that kernel
+ * waits for everything before it on the stream before it reads or writes anything,
+ * so callers need do nothing.  The split-KV attention kernels trigger their
+ * dependents as soon as they start: this only matters to a caller that launches
+ * its OWN next kernel with that attribute -- such a kernel must call
+ * cudaGridDependencySynchronize() (griddepcontrol.wait) before it reads `out`.
+ * Kernels launched the ordinary way are ordered as always.
  */
 #ifndef QWENGINE_ATTN_H_
 #define QWENGINE_ATTN_H_

@@ -401,9 +401,9 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
   if ((d->flags & QW_F_NO_CAUSAL) && (d->flags & QW_F_ROPE) && !d->q_pos && !d->mpos) return QW_ERR_ARG;
   if (d->flags & QW_F_NO_ATTENTION) {  // rope(k) + append only
     if (partial) return QW_ERR_ARG;
-    rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
-        d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
-        (d->flags & QW_F_ROPE) ? 1 : 0, tab, nullptr, 0, pm, d->q_pos);
+    launch_kernel(rope_append_kernel, dim3((unsigned)((size_t)d->n_seq * d->n_new)), dim3(128), 0, st, true, d->k_new,
+                  d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
+                  (d->flags & QW_F_ROPE) ? 1 : 0, tab, static_cast<int *>(nullptr), 0, pm, d->q_pos);
     return check_launch("rope_append_kernel");
   }
   const bool use_umma =
@@ -435,21 +435,21 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
     uint16_t *qo = const_cast<uint16_t *>(d->q), *go = const_cast<uint16_t *>(d->gate);
     const int do_rope = (d->flags & QW_F_ROPE) ? 1 : 0;
     if (fr->is_f32)
-      fused_rows_kernel<float><<<dim3(rows, (unsigned)d->kv_heads), 256, 0, st>>>(
-          static_cast<const float *>(fr->rows), fr->q_norm_w, fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
-          d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt, n_zero, pm, d->q_pos);
+      launch_kernel(fused_rows_kernel<float>, dim3(rows, (unsigned)d->kv_heads), dim3(256), 0, st, true,
+                    static_cast<const float *>(fr->rows), fr->q_norm_w, fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
+                    d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt, n_zero, pm, d->q_pos);
     else
-      fused_rows_kernel<uint16_t><<<dim3(rows, (unsigned)d->kv_heads), 256, 0, st>>>(
-          static_cast<const uint16_t *>(fr->rows), fr->q_norm_w, fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
-          d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt, n_zero, pm, d->q_pos);
+      launch_kernel(fused_rows_kernel<uint16_t>, dim3(rows, (unsigned)d->kv_heads), dim3(256), 0, st, true,
+                    static_cast<const uint16_t *>(fr->rows), fr->q_norm_w, fr->k_norm_w, fr->eps, qo, go, d->kc, d->vc, d->pos,
+                    d->cache_row, d->mpos, d->n_new, d->q_heads, d->kv_heads, do_rope, tab, cnt, n_zero, pm, d->q_pos);
     int rc = check_launch("fused_rows_kernel");
     if (rc) return rc;
     appended = true;
   } else if (d->flags & QW_F_APPEND) {
     prefer_max_shared_once();
-    rope_append_kernel<<<(unsigned)((size_t)d->n_seq * d->n_new), 128, 0, st>>>(
-        d->k_new, d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
-        (d->flags & QW_F_ROPE) ? 1 : 0, tab, cnt, n_zero, pm, d->q_pos);
+    launch_kernel(rope_append_kernel, dim3((unsigned)((size_t)d->n_seq * d->n_new)), dim3(128), 0, st, true, d->k_new,
+                  d->v_new, d->kc, d->vc, d->pos, d->cache_row, d->mpos, d->n_new, d->kv_heads,
+                  (d->flags & QW_F_ROPE) ? 1 : 0, tab, cnt, n_zero, pm, d->q_pos);
     int rc = check_launch("rope_append_kernel");
     if (rc) return rc;
     appended = true;

@@ -192,11 +192,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   }
   return false;
 }
-// Programmatic dependent launch.  The append kernel of a step calls grid_dep_launch_dependents() first thing,
-// which lets the attention kernel launched behind it (with the stream-serialisation attribute) start while
-// the append still runs; the attention kernel calls grid_dep_wait() only where it first needs the append's
-// results: before it loads a tile that holds new rows, and before it takes an arrival ticket (the append
-// kernel clears the counters).  Without the launch attribute both are no-ops.
+// Programmatic dependent launch.  The append kernel of a step is launched as a programmatic dependent: it waits
+// (grid_dep_wait) for whatever ran before it on the stream, then calls grid_dep_launch_dependents(), which lets the
+// attention kernel launched behind it (with the stream-serialisation attribute) start while the append still runs;
+// the attention kernel calls grid_dep_wait() only where it first needs the append's results: before it loads a
+// tile that holds new rows, and before it takes an arrival ticket (the append kernel clears the counters).  The
+// attention kernels call grid_dep_launch_dependents() first thing as well, so that the NEXT launch on the stream, if
+// it is a programmatic dependent (this library's append kernel of the next call is), is resident and waiting when
+// they end instead of being launched then.  Without the launch attribute both instructions are no-ops.
 __device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -69,6 +69,10 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const uint16_t *k_new,
                                                           const int *mpos, int n_new, int kv_heads, int do_rope,
                                                           const __grid_constant__ RopeTable tab, int *zero_ints,
                                                           int n_zero, PageMap pages, const int *q_pos) {
+  // Launched as a programmatic dependent itself: an attention kernel of this library that ran before it on the
+  // stream lets it become resident early (its launch latency then overlaps that kernel), and it waits here until
+  // whatever ran before has completed and is visible -- before it reads or writes anything.
+  grid_dep_wait();
   grid_dep_launch_dependents();  // the attention launch behind this one may start now; it waits where it must
   // block 0 also clears the split-KV arrival counters of the attention launch that follows
   if (blockIdx.x == 0)
@@ -126,6 +130,10 @@ __global__ void __launch_bounds__(256) fused_rows_kernel(const TIn *fused, const
                                                          int q_heads, int kv_heads, int do_rope,
                                                          const __grid_constant__ RopeTable tab, int *zero_ints,
                                                          int n_zero, PageMap pages, const int *q_pos) {
+  // Launched as a programmatic dependent itself: an attention kernel of this library that ran before it on the
+  // stream lets it become resident early (its launch latency then overlaps that kernel), and it waits here until
+  // whatever ran before has completed and is visible -- before it reads or writes anything.
+  grid_dep_wait();
   grid_dep_launch_dependents();  // the attention launch behind this one may start now; it waits where it must
   if (blockIdx.x == 0 && blockIdx.y == 0)
     for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero_ints[i] = 0;

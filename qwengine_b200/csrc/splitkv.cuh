@@ -459,6 +459,9 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
   const int cta = blockIdx.x;
+  // a kernel launched behind this one as a programmatic dependent (this library's append kernel is) may become
+  // resident now; it waits for this grid's completion before it touches memory
+  grid_dep_launch_dependents();
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], NCW); }

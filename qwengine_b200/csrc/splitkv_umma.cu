@@ -82,6 +82,9 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
   const int cta = blockIdx.x;
+  // a kernel launched behind this one as a programmatic dependent (this library's append kernel is) may become
+  // resident now; it waits for this grid's completion before it touches memory
+  grid_dep_launch_dependents();
 
   if (tid == 0) {
     // the softmax warps signal once per warp (each lane's fence, __syncwarp, then lane 0 arrives): 512 arrivals on
