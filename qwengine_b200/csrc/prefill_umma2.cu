@@ -240,6 +240,9 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
   const uint32_t rank = cluster_ctarank();  // 0 = leader (issues the MMAs), 1 = peer
   const bool leader = rank == 0;
   const int cluster = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  // a kernel launched behind this one as a programmatic dependent (the append kernel of the next chunk is) may
+  // become resident now; it waits for this grid's completion before it touches memory
+  grid_dep_launch_dependents();
 
   if (tid == 0) {
     mbar_init(&ctl->q_full, 1);
