@@ -184,18 +184,25 @@ int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKV
   // folded, with Q fragments in registers, config 2 took 140 us instead of 104 us.
   constexpr bool FOLD = MT > 1;
   auto kern = splitkv_kernel<MT, DS, STAGES, LOK, FOLD, TIn, TOut>;
+  // Few long units on the whole device (one to four sequences decoding alone: every unit is cut into eight parts or
+  // more): the variant whose CTAs merge a unit together, a slice each.  It needs the whole grid resident at once,
+  // which one CTA per SM on a grid of the SM count is.
+  constexpr bool HAS_SLICED = MT == 1;
+  auto kern_sliced = splitkv_kernel<MT, DS, STAGES, LOK, FOLD, TIn, TOut, HAS_SLICED>;
   constexpr size_t smem = splitkv_smem_bytes<MT, DS, STAGES>();
   static std::atomic<int> configured[MAX_DEVICES];
   int rc = once_per_device(configured, [&]() -> int {
     QW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (HAS_SLICED) QW_CUDA(cudaFuncSetAttribute(kern_sliced, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     return QW_OK;
   });
   if (rc) return rc;
   g_attn_kernel = "splitkv_kernel";
+  const bool sliced = HAS_SLICED && p.cnt && p.G == sm_count() && 8ll * p.n_seq * p.nblk * p.kv_heads <= p.G;
   prof_mark(0, st);
   // behind this step's append kernel the launch is a programmatic dependent: it starts while that one still runs
-  const cudaError_t le =
-      launch_kernel(kern, dim3(p.G), dim3((SK_KS * DS + (FOLD ? 0 : 1)) * 32), smem, st, pdl, mk, mv, p);
+  const cudaError_t le = launch_kernel(sliced ? kern_sliced : kern, dim3(p.G), dim3((SK_KS * DS + (FOLD ? 0 : 1)) * 32),
+                                       smem, st, pdl, mk, mv, p);
   prof_mark(1, st);
   if (le != cudaSuccess) {
     ++g_launches;

@@ -425,11 +425,106 @@ __device__ __forceinline__ bool merge_unit_bulk(const SplitKVParams &p, int u, i
   return ok;
 }
 
+// Merge of one unit by ALL the CTAs that hold a part of it, each taking a slice of the (row, 4-channel) items: for
+// a unit cut into dozens of parts (one sequence alone on the whole device: 37) a single merging CTA has to pull every
+// part -- 231 KB -- through one SM, which costs more than the streaming of the sequence's KV; sliced, a CTA reads
+// 1/nparts of every part.  The caller has waited until every part has arrived.  One warp per item, lanes over the
+// parts (up to five each): all loads of two items are in flight together, then the row maximum, the weights and
+// the weighted sums are reduced across the lanes in a fixed tree, so the result does not depend on timing.
+// j: this CTA's index among the unit's nparts CTAs (nparts <= 160).
+template <typename TOut>
+__device__ __forceinline__ void merge_unit_sliced(const SplitKVParams &p, int u, int c_first, int nparts, int j, int warp,
+                                                  int lane, int nwarps) {
+  const int kvh = u % p.kv_heads, sb = u / p.kv_heads, blk = sb % p.nblk, s = sb / p.nblk;
+  const int tok0 = blk * p.rb, ntok = min(p.rb, p.n_new - tok0);
+  const int R = ntok * GROUP, rs = p.rb * GROUP, n_items = R * 64;
+  const int lo = (int)((long long)n_items * j / nparts), hi = (int)((long long)n_items * (j + 1) / nparts);
+  const float *base = p.ws + (size_t)(c_first + u) * rs * PART_STRIDE;  // part k, row r: base + (k * rs + r) * PART_STRIDE
+  constexpr int PL = 5;
+  for (int it0 = lo + warp * 2; it0 < hi; it0 += nwarps * 2) {
+    float m[2][PL], l[2][PL];
+    float4 v[2][PL];
+    uint2 g2[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int item = it0 + e, r = item >> 6, c4 = item & 63;
+      g2[e] = make_uint2(0, 0);
+#pragma unroll
+      for (int q = 0; q < PL; ++q) {
+        const int k = lane + 32 * q;
+        m[e][q] = -INFINITY;
+        l[e][q] = 0.f;
+        v[e][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (item < hi && k < nparts) {
+          const float *src = base + ((size_t)k * rs + r) * PART_STRIDE;
+          m[e][q] = __ldcg(src + 256);
+          l[e][q] = __ldcg(src + 257);
+          v[e][q] = __ldcg(reinterpret_cast<const float4 *>(src + c4 * 4));
+        }
+      }
+      if (item < hi && lane == 0 && !p.partial_out && p.do_gate) {
+        const size_t gr = ((size_t)s * p.n_new + tok0 + r / GROUP) * p.q_heads + (size_t)kvh * GROUP + r % GROUP;
+        g2[e] = *reinterpret_cast<const uint2 *>(p.gate + gr * HEAD_DIM + c4 * 4);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int item = it0 + e, r = item >> 6, c4 = item & 63;
+      if (item >= hi) continue;  // uniform over the warp
+      float m_run = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < PL; ++q) m_run = fmaxf(m_run, l[e][q] > 0.f ? m[e][q] : -INFINITY);
+#pragma unroll
+      for (int o = 16; o; o >>= 1) m_run = fmaxf(m_run, __shfl_xor_sync(0xffffffffu, m_run, o));
+      float l_run = 0.f;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int q = 0; q < PL; ++q) {
+        const float f = l[e][q] > 0.f ? fast_exp2(m[e][q] - m_run) : 0.f;
+        l_run = fmaf(l[e][q], f, l_run);
+        a.x = fmaf(v[e][q].x, f, a.x); a.y = fmaf(v[e][q].y, f, a.y);
+        a.z = fmaf(v[e][q].z, f, a.z); a.w = fmaf(v[e][q].w, f, a.w);
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
+        a.x += __shfl_xor_sync(0xffffffffu, a.x, o); a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
+        a.z += __shfl_xor_sync(0xffffffffu, a.z, o); a.w += __shfl_xor_sync(0xffffffffu, a.w, o);
+      }
+      if (lane != 0) continue;
+      const size_t gr = ((size_t)s * p.n_new + tok0 + r / GROUP) * p.q_heads + (size_t)kvh * GROUP + r % GROUP;
+      if (p.partial_out) {
+        float *dst = p.partial_out + gr * PART_STRIDE;
+        *reinterpret_cast<float4 *>(dst + c4 * 4) = a;
+        if (c4 == 0) { dst[256] = m_run; dst[257] = l_run; }
+        continue;
+      }
+      const float inv = __fdividef(1.f, l_run);
+      a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
+      if (p.do_gate) {
+        a.x *= sigmoid_fast(bf16lo(g2[e].x)); a.y *= sigmoid_fast(bf16hi(g2[e].x));
+        a.z *= sigmoid_fast(bf16lo(g2[e].y)); a.w *= sigmoid_fast(bf16hi(g2[e].y));
+      }
+      if constexpr (sizeof(TOut) == 4) {
+        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + gr * HEAD_DIM + c4 * 4) = a;
+      } else {
+        *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.out) + gr * HEAD_DIM + c4 * 4) =
+            make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
+      }
+      if (c4 == 0 && p.lse) p.lse[gr] = (m_run + log2f(l_run)) * LN2;
+    }
+  }
+}
+
 // FOLD = false: a dedicated producer warp (warp NCW).  FOLD = true: lane 0 of consumer warp 0 also
 // issues the TMA loads, STAGES - 1 tiles ahead of the tile it is about to consume; the block is then
 // exactly 8 warps and every thread may use up to 255 registers (with a ninth warp the register file
 // is carved as if for twelve, which caps a thread at 168 and makes the two-row-tile variant spill).
-template <int MT, int DS, int STAGES, int LOK, bool FOLD, typename TIn, typename TOut>
+// SLICED: units cut across CTAs are merged by all of their CTAs together, each a slice of the channels (see
+// merge_unit_sliced), instead of by the CTA that arrives last.  Every CTA then waits (bounded) for the unit's arrival
+// counter to reach the number of parts, which needs all CTAs of the grid resident at once -- one per SM, as the grid
+// is sized -- so the host selects this variant only where it pays: few long units, each cut into eight parts or more.
+template <int MT, int DS, int STAGES, int LOK, bool FOLD, typename TIn, typename TOut, bool SLICED = false>
 __global__ void __launch_bounds__((SK_KS * DS + (FOLD ? 0 : 1)) * 32, 1)
 splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                const __grid_constant__ SplitKVParams p) {
@@ -454,7 +549,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   long long *seg = reinterpret_cast<long long *>(empty + STAGES);  // [0]=total [1]=pre(u_first) [2]=u_first
   volatile int *ticket = reinterpret_cast<volatile int *>(seg + 3);
   uint64_t *merge_bar = reinterpret_cast<uint64_t *>(seg + 4);  // two: bulk copies of a merge's parts land on them
-  volatile int *pend = reinterpret_cast<volatile int *>(seg + 6);  // units this CTA is to merge, and [8] their count
+  volatile int *pend = reinterpret_cast<volatile int *>(seg + 6);  // units this CTA is to merge: 5 ints each, [10] their count, [11] scratch
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = p.n_seq * p.nblk * p.kv_heads;
@@ -467,7 +562,7 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], NCW); }
     mbar_init(merge_bar, 1);
     mbar_init(merge_bar + 1, 1);
-    pend[8] = 0;
+    pend[10] = 0;
     fence_barrier_init();
     prefetch_tensormap(&mapK);
     prefetch_tensormap(&mapV);
@@ -953,24 +1048,48 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       // a chain of round trips several times longer than the streaming of its KV).  Which way a unit is merged
       // must not depend on which CTA happens to arrive last -- the two ways round differently -- and with the
       // merge deferred it depends on the shapes alone.  A slice has at most two cut units: its first and its last.
-      // The notes -- (unit, first CTA, last CTA, parts) each and their count -- live in shared memory: the tile
-      // loop has no register to spare for them.
-      if (tid == 0 && *ticket == nparts - 1 && pend[8] < 2) {
-        const int n = pend[8];
-        pend[4 * n] = u; pend[4 * n + 1] = c_first; pend[4 * n + 2] = c_last; pend[4 * n + 3] = nparts;
-        pend[8] = n + 1;
+      // The notes -- (unit, first CTA, last CTA, parts, arrived last) each and their count -- live in shared memory:
+      // the tile loop has no register to spare for them.  The sliced variant notes every cut unit: all of a unit's
+      // CTAs take part in its merge.
+      const bool sliced = SLICED && total >= (long long)G && nparts <= 160;
+      if (tid == 0 && (sliced || *ticket == nparts - 1) && pend[10] < 2) {
+        const int n = pend[10];
+        pend[5 * n] = u; pend[5 * n + 1] = c_first; pend[5 * n + 2] = c_last; pend[5 * n + 3] = nparts;
+        pend[5 * n + 4] = (*ticket == nparts - 1) ? 1 : 0;
+        pend[10] = n + 1;
       }
     }
     pre += nt_unit;
     ++u;
   }
   consumer_sync(NCT);  // thread 0's notes above
-  const int n_pend = pend[8];
+  const int n_pend = pend[10];
   uint32_t merge_phase = 0;
   for (int k = 0; k < n_pend; ++k) {
     constexpr uint32_t MERGE_BUF = (uint32_t)(STAGES * SK_STAGE_BYTES + QREGION);
-    const int um = pend[4 * k], cf = pend[4 * k + 1], cl = pend[4 * k + 2], np = pend[4 * k + 3];
+    const int um = pend[5 * k], cf = pend[5 * k + 1], cl = pend[5 * k + 2], np = pend[5 * k + 3];
     const int R = min(p.rb, p.n_new - ((um / p.kv_heads) % p.nblk) * p.rb) * GROUP;
+    if (SLICED && total >= (long long)G && np <= 160) {
+      // every CTA of the unit has taken its ticket before it waits here, so the count is reached as soon as the
+      // slowest of them is through its tiles; the wait is bounded all the same
+      if (tid == 0) {
+        const uint64_t t0 = global_timer_ns();
+        int got = 1;
+        for (;;) {
+          int v;
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.cnt + um) : "memory");
+          if (v >= np) break;
+          if (global_timer_ns() - t0 > WAIT_LIMIT_NS) { got = 0; break; }
+        }
+        pend[11] = got;
+      }
+      consumer_sync(NCT);
+      if (pend[11]) merge_unit_sliced<TOut>(p, um, cf, np, cta - cf, warp, lane, NCW);
+      else if (tid == 0 && p.status) *p.status = DEV_ERR_FULL_WAIT;
+      consumer_sync(NCT);  // pend[11] is written again for the next unit
+      continue;            // the counter is left as it is: other CTAs of the unit may still be reading it
+    }
+    if (!pend[5 * k + 4]) continue;  // (sliced variant, unit merged the plain way: not this CTA's)
     if (total >= (long long)G && merge_bulk_fits(p, R, np, MERGE_BUF)) {
       if (!merge_unit_bulk<TOut>(p, um, cf, np, tid, NCT, smem, MERGE_BUF, merge_bar, merge_phase) && tid == 0 && p.status)
         *p.status = DEV_ERR_FULL_WAIT;
