@@ -945,7 +945,27 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
 #pragma unroll
         for (int n = 0; n < NT_O; ++n) { o[mt][n][2 * h2] *= f; o[mt][n][2 * h2 + 1] *= f; }
       }
-    for (int k = 0; k < SK_KS; ++k) {
+    // In the CTA's last segment the K/V ring is idle: every key slice writes its sums into a buffer of its own
+    // there and the finishing loop adds the four up, in slice order -- the same additions in the same order as the
+    // rounds below, so the same bits -- with one barrier instead of four rounds through one buffer.
+    const bool last_seg = pre + nt_unit >= g1;
+    if (last_seg) {
+      float *cb = reinterpret_cast<float *>(stage_base) + ks * (ROWS * HEAD_DIM);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int row = mt * 16 + h2 * 8 + qd;
+#pragma unroll
+          for (int n = 0; n < NT_O; ++n) {
+            const int d = ds * DW + n * 8 + ql * 2;
+            *reinterpret_cast<float2 *>(cb + row * HEAD_DIM + (d ^ ((row & 7) << 3))) =
+                make_float2(o[mt][n][2 * h2], o[mt][n][2 * h2 + 1]);
+          }
+        }
+      consumer_sync(NCT);
+    }
+    for (int k = 0; k < SK_KS && !last_seg; ++k) {
       if (ks == k) {
         // all loads of the round first, then all stores: read-add-write per element would serialise on
         // shared-memory latency (32 dependent round trips per thread and round)
@@ -990,8 +1010,17 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       float lg = 0.f;
 #pragma unroll
       for (int k = 0; k < SK_KS; ++k) lg += lx[k * ROWS + row] * fast_exp2(mx[k * ROWS + row] - m_use);
-      const float4 *srcp = reinterpret_cast<const float4 *>(comb + row * HEAD_DIM + ((c8 * 8) ^ ((row & 7) << 3)));
-      const float4 a = srcp[0], bq = srcp[1];
+      const float4 *srcp = reinterpret_cast<const float4 *>((last_seg ? reinterpret_cast<const float *>(stage_base) : comb) +
+                                                            row * HEAD_DIM + ((c8 * 8) ^ ((row & 7) << 3)));
+      float4 a = srcp[0], bq = srcp[1];
+      if (last_seg) {
+#pragma unroll
+        for (int k = 1; k < SK_KS; ++k) {
+          const float4 wa = srcp[k * (ROWS * HEAD_DIM / 4)], wb = srcp[k * (ROWS * HEAD_DIM / 4) + 1];
+          a.x += wa.x; a.y += wa.y; a.z += wa.z; a.w += wa.w;
+          bq.x += wb.x; bq.y += wb.y; bq.z += wb.z; bq.w += wb.w;
+        }
+      }
       float v[8] = {a.x, a.y, a.z, a.w, bq.x, bq.y, bq.z, bq.w};
       const int b = row / GROUP, hh = row % GROUP;
       const size_t grow = ((size_t)ui.s * p.n_new + ui.tok0 + b) * p.q_heads + (size_t)ui.kvh * GROUP + hh;
