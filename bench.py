@@ -544,8 +544,8 @@ def measure_decode_b1(args, peaks):
     the reference runs its decode step (src/model.cu:318-327) and takes the host's launch cost out."""
     from qwengine_b200 import api
     res = {}
-    for hist in (8192, 32768):
-        w = make_batch("decode_b1", [hist], 1, 4, args.seed + 21)
+    for hist, n_new in ((8192, 1), (32768, 1), (8192, 4), (32768, 4)):
+        w = make_batch("decode_b1", [hist], n_new, 4, args.seed + 21)
         mx = bind_fused(api, w)
         ms = timed(mx.forward, args.steps, 5, args.repeats, 1)
         mx.check_status()
@@ -560,13 +560,15 @@ def measure_decode_b1(args, peaks):
         ms_g = timed(g.replay, args.steps, 5, args.repeats, 1)
         mx.check_status()
         us, us_g = float(np.median(ms)) * 1e3, float(np.median(ms_g)) * 1e3
-        res["hist_%d" % hist] = {"us_per_step": round(us_g, 2), "us_per_step_python_launch": round(us, 2),
+        res[("hist_%d" if n_new == 1 else "verify4_hist_%d") % hist] = {
+                                 "us_per_step": round(us_g, 2), "us_per_step_python_launch": round(us, 2),
                                  "us_stats": {k: (round(v * 1e3, 2) if k != "repeats" else v) for k, v in stats(ms_g).items()},
                                  "kv_GBps": round(w["kv_bytes"] / (us_g * 1e-6) / 1e9, 1),
                                  "hbm_frac": round(w["kv_bytes"] / (us_g * 1e-6) / 1e9 / peaks[0], 4),
                                  "kernel": api.last_attention_kernel()}
-    res["what"] = ("one sequence x 1 new token, fused call (2 launches) replayed as a CUDA graph; latency-bound: "
-                   "33.6 MB / 134 MB of KV per step")
+    res["what"] = ("one sequence x 1 new token (hist_*) or x 4 draft tokens (verify4_hist_*, the reference's MTP verify), "
+                   "fused call (2 launches) replayed as a CUDA graph, and launched from the host step by step; "
+                   "latency-bound: 33.6 MB / 134 MB of KV per step")
     return res
 
 

@@ -171,7 +171,15 @@ enum {
                           and workspace are not touched and may be NULL).  For a rank that holds a whole
                           chunk's keys but computes only some of its query rows (query-row split of one
                           sequence over a GPU pair): it appends the chunk once, then attends per row block
-                          without QW_F_APPEND                                                        */
+                          without QW_F_APPEND                                                        */,
+  QW_F_NO_GRID_WAIT = 512 /* never pick a kernel whose CTAs wait for one another.  One to four sequences decoding
+                          alone are served by a variant in which all CTAs of a KV head merge its result together
+                          once every part has arrived (a bounded wait on an arrival counter); that needs the whole
+                          grid -- one CTA per SM -- resident at once, which it is unless ANOTHER kernel that
+                          holds SMs for as long runs beside it on the same GPU (two such calls on two streams can
+                          starve each other: the wait then runs out after 0.2 s and *status is set).  A caller
+                          that runs attention calls concurrently on one GPU sets this flag; it costs 4 to 5 us
+                          of the 21 us such a call takes                                               */
 };
 
 typedef struct qw_mixer_desc {

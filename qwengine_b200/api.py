@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libqwengine_attn.so")
 
 QW_OK = 0
-F_ROPE, F_APPEND, F_GATE, F_OUT_F32, F_NO_UMMA, F_FAST_P, F_NO_CAUSAL, F_NO_ATTENTION = 1, 2, 4, 8, 16, 32, 128, 256
+F_ROPE, F_APPEND, F_GATE, F_OUT_F32, F_NO_UMMA, F_FAST_P, F_NO_CAUSAL, F_NO_ATTENTION, F_NO_GRID_WAIT = 1, 2, 4, 8, 16, 32, 128, 256, 512
 PARTIAL_FLOATS = 260
 HEAD_DIM, ROTARY_DIM, GROUP = 256, 64, 6
 

@@ -168,6 +168,7 @@ struct AttnCall {
   bool do_rope, do_gate, no_causal;
   bool q_dep;  // q / gate are produced by the launch before the attention kernel (fused projection rows)
   bool pdl;    // the launch right before the attention kernel is this call's append kernel: overlap with it
+  bool no_grid_wait;  // QW_F_NO_GRID_WAIT: no kernel variant whose CTAs wait for one another
   float *ws;
   size_t ws_floats;
   int *cnt;  // zeroed arrival counters (one per unit) or null
@@ -178,7 +179,8 @@ int splitkv_rb(int n_new) { return n_new < 5 ? n_new : 5; }  // tokens per unit:
 size_t splitkv_slot_floats(int rb) { return (size_t)rb * GROUP * PART_STRIDE; }
 
 template <int MT, int DS, int STAGES, int LOK, typename TIn, typename TOut>
-int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, cudaStream_t st, bool pdl) {
+int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p, cudaStream_t st, bool pdl,
+                     bool no_grid_wait) {
   // The 8-warp block (producer folded into warp 0) leaves every thread up to 255 registers, which the
   // two-row-tile variant needs.  The one-tile variant is faster with its dedicated producer warp:
   // folded, with Q fragments in registers, config 2 took 140 us instead of 104 us.
@@ -198,7 +200,7 @@ int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKV
   });
   if (rc) return rc;
   g_attn_kernel = "splitkv_kernel";
-  const bool sliced = HAS_SLICED && p.cnt && p.G == sm_count() && 8ll * p.n_seq * p.nblk * p.kv_heads <= p.G;
+  const bool sliced = HAS_SLICED && !no_grid_wait && p.cnt && p.G == sm_count() && 8ll * p.n_seq * p.nblk * p.kv_heads <= p.G;
   prof_mark(0, st);
   // behind this step's append kernel the launch is a programmatic dependent: it starts while that one still runs
   const cudaError_t le = launch_kernel(sliced ? kern_sliced : kern, dim3(p.G), dim3((SK_KS * DS + (FOLD ? 0 : 1)) * 32),
@@ -221,12 +223,12 @@ int launch_splitkv_t(const CUtensorMap &mk, const CUtensorMap &mv, const SplitKV
 template <int MT, int STAGES>
 int launch_splitkv_mt(const AttnCall &c, const CUtensorMap &mk, const CUtensorMap &mv, const SplitKVParams &p,
                       cudaStream_t st) {
-  if (c.q_is_f32) return launch_splitkv_t<MT, 2, STAGES, 16, float, float>(mk, mv, p, st, c.pdl);
+  if (c.q_is_f32) return launch_splitkv_t<MT, 2, STAGES, 16, float, float>(mk, mv, p, st, c.pdl, c.no_grid_wait);
   if (c.out_is_f32)
-    return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, float>(mk, mv, p, st, c.pdl)
-                     : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, float>(mk, mv, p, st, c.pdl);
-  return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, uint16_t>(mk, mv, p, st, c.pdl)
-                   : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, uint16_t>(mk, mv, p, st, c.pdl);
+    return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, float>(mk, mv, p, st, c.pdl, c.no_grid_wait)
+                     : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, float>(mk, mv, p, st, c.pdl, c.no_grid_wait);
+  return c.do_rope ? launch_splitkv_t<MT, 2, STAGES, 4, uint16_t, uint16_t>(mk, mv, p, st, c.pdl, c.no_grid_wait)
+                   : launch_splitkv_t<MT, 2, STAGES, 0, uint16_t, uint16_t>(mk, mv, p, st, c.pdl, c.no_grid_wait);
 }
 
 int launch_splitkv(const AttnCall &c, cudaStream_t st) {
@@ -320,6 +322,8 @@ int launch_splitkv_umma_call(const AttnCall &c, cudaStream_t st) {
   if (max_slots - n_units < G) G = max_slots - n_units;
   if (G < 1) return QW_ERR_WORKSPACE;
   p.G = (int)G;
+  // few long units on the whole device: all CTAs of a unit merge it together (see splitkv_kernel's sliced variant)
+  p.sliced = (!c.no_grid_wait && c.cnt && p.G == sm_count() && 8 * n_units <= p.G) ? 1 : 0;
   p.q_lo_dims = c.do_rope ? ROTARY_DIM : 0;
   p.scale_log2 = c.scale * LOG2E;
   p.do_rope = c.do_rope; p.do_gate = c.do_gate && c.gate; p.no_causal = c.no_causal; p.q_dep = c.q_dep;
@@ -497,6 +501,7 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
   c.no_causal = (d->flags & QW_F_NO_CAUSAL) != 0;
   c.q_dep = fr != nullptr;
   c.pdl = appended;
+  c.no_grid_wait = (d->flags & QW_F_NO_GRID_WAIT) != 0;
   c.ws = ws;
   c.ws_floats = ws_floats;
   c.cnt = cnt;

@@ -52,6 +52,7 @@ struct SplitKVParams {
   int do_rope, do_gate;
   int q_rows_pad;         // tcgen05 kernel: rows of the Q tile that really exist in shared memory (32, 64 or 128)
   int nslot;              // tcgen05 kernel: 16 KB ring slots that fit beside that Q tile
+  int sliced;             // tcgen05 kernel: all CTAs of a cut unit merge it together, a slice each (see merge_unit_sliced)
   int q_dep;              // q and gate are written by the launch before this one (fused projection rows)
   int no_causal;          // every row sees exactly pos[s] keys (a KV sub-range without the new rows)
   RopeTable rope;

@@ -617,6 +617,29 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
       asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
       uint32_t merge_phase = 0;
       for (int k = 0; k < n_pend && ctl->merge_go; ++k) {
+        if (p.sliced && all_live && ctl->merge_parts[k] <= 160) {
+          // Few long units (one sequence's draft tokens on the whole device): every CTA of the unit merges a slice
+          // of its channels once all parts have arrived.  All of them have taken their tickets before they wait
+          // here; the wait is bounded all the same.
+          if (st_tid == 0) {
+            const uint64_t t0 = global_timer_ns();
+            int got = 1;
+            for (;;) {
+              int v;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.cnt + pend_u[k]) : "memory");
+              if (v >= ctl->merge_parts[k]) break;
+              if (*abort_flag || global_timer_ns() - t0 > WAIT_LIMIT_NS) { got = 0; break; }
+            }
+            ctl->merge_go = got;
+            if (!got) fail(DEV_ERR_SOFTMAX_WAIT);
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+          if (ctl->merge_go)
+            merge_unit_sliced<TOut>(p, pend_u[k], pend_cf[k], ctl->merge_parts[k], cta - pend_cf[k],
+                                    warp - DU_CTL_THREADS / 32, lane, DU_SM_THREADS / 32);
+          asm volatile("bar.sync 1, %0;" ::"n"(DU_SM_THREADS) : "memory");
+          continue;  // the counter is left as it is: other CTAs of the unit may still be reading it
+        }
         if (ctl->ticket[k] == ctl->merge_parts[k] - 1) {
           const int c_first = pend_cf[k], c_last = pend_cl[k];
           const int blk = (pend_u[k] / p.kv_heads) % p.nblk;  // no load on the way to the merge: unit_info reads pos

@@ -117,6 +117,24 @@ def test_uniform_batches_that_give_every_unit_two_ctas(n_seq, hist):
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
 
 
+@pytest.mark.parametrize("hist", [[5000], [3000, 2000], [40000]])
+def test_few_long_sequences_merge_sliced_or_by_the_last_cta(hist):
+    """One to four sequences decoding alone: every KV head is cut into eight parts or more and all of its CTAs merge
+    it together, a slice of the channels each.  With QW_F_NO_GRID_WAIT the CTA that arrives last merges alone.  Both
+    against the oracle; each bit-identical from run to run."""
+    c = Case(60 + len(hist), hist, 1)
+    _full_check(c, "sliced merge hist=%s" % hist)
+    ref, lse_ref, _, _ = c.oracle()
+    fl = api.F_ROPE | api.F_APPEND | api.F_GATE | api.F_NO_GRID_WAIT
+    a = run_case(c, out_f32=True, flags=fl)
+    b = run_case(c, out_f32=True, flags=fl)
+    check_out(a[0], ref, "no grid wait")
+    check_lse(a[1], lse_ref, "no grid wait")
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    s1, s2 = run_case(c, out_f32=True), run_case(c, out_f32=True)
+    assert np.array_equal(s1[0], s2[0]) and np.array_equal(s1[1], s2[1])
+
+
 def test_config3_shape_reduced():
     """BASELINE config 3 shape: 8 sequences x 4 draft tokens, ragged histories."""
     rng = np.random.default_rng(41)
