@@ -94,7 +94,10 @@ int qw_kv_append_f32(const float *k, const float *v, qw_bf16 *kc, qw_bf16 *vc,
  * even hold one CTA's partial (ctx below about 128) the call returns QW_ERR_WORKSPACE.
  * ctx is the number of rows in kc / vc.  1 <= B <= 8.  The bf16 flavour runs B >= 2 on the
  * tcgen05 split-KV kernel; the fp32 flavour keeps q exact (bf16 hi + lo on all channels)
- * on the mma.sync kernel.
+ * on the mma.sync kernel.  These launchers serve one sequence, so they take the kernel variant
+ * whose CTAs merge a KV head together (see QW_F_NO_GRID_WAIT below): run them on one stream per
+ * GPU at a time, as the reference does; an engine that overlaps attention calls on one GPU uses
+ * qw_mixer_forward with that flag instead.
  * Replaces k_attn_decode<<<dim3(q_heads, B), 256>>>: src/mixers.cu:436-525;
  * launched at src/model.cu:236-238, src/mtp.cu:176-178. */
 int qw_attn_decode_bf16(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf16 *vc, qw_bf16 *out,
