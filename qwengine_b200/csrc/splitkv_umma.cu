@@ -34,7 +34,7 @@ constexpr int DU_MAX_SLOT = 6;             // ring slots when the Q tile is smal
 constexpr int DU_SMEM_TOTAL = 232448 - 1024;   // dynamic shared memory left after the alignment slack
 constexpr int DU_NWG = 4;
 constexpr int DU_MAX_PARTS = 256;         // CTAs of one unit whose liveness is tabulated for the merge
-constexpr int DU_SWITCH_TILES = 8;        // tiles of time charged to a CTA whose slice crosses into the next unit
+constexpr int DU_SWITCH_TILES = 12;        // tiles of time charged to a CTA whose slice crosses into the next unit
 constexpr int DU_SM_THREADS = DU_NWG * 128;
 constexpr int DU_CTL_THREADS = 128;        // control warpgroup: TMA producer, MMA issuer, the partition warp, one idle warp
 constexpr int DU_THREADS = DU_CTL_THREADS + DU_SM_THREADS;
@@ -113,7 +113,10 @@ splitkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_const
     // to four tiles, measured; and it is usually the last to arrive at both of its units, so it merges
     // both, one after the other, at the very end of the kernel.  The flat list charges for it: every unit
     // is preceded by `lead` entries that stand for no tile, so such a CTA receives that many tiles less.
-    // Measured on the ragged verify batch: 5 entries 0.140 ms, 7 0.137, 9 0.131-0.134, 12 0.132.
+    // Measured on the ragged verify batch (kernel, two boxes): 5 entries 0.140 ms, 7 0.137-0.139, 9 0.131-0.135,
+    // 11 0.135, 13 0.131-0.133, 15 0.129-0.130, 17 0.129-0.131, 21 0.133.  13 is used: beyond it the gain is the
+    // batch's own (its boundary CTAs stop being the last at both of their units), and a batch of many short
+    // units would be charged more than a boundary costs.
     total += (long long)lead * live;
     int u0 = n_units; long long pre0 = 0;
     if (cta < geff) warp_find_unit<DU_BN>(p, n_units, lane, total * cta / geff, u0, pre0, lead);
