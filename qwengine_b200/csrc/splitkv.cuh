@@ -426,6 +426,68 @@ __device__ __forceinline__ bool merge_unit_bulk(const SplitKVParams &p, int u, i
   return ok;
 }
 
+// Merge of a unit cut into at most four parts, straight from the workspace: thread = (row, 8 channels), every load
+// of every part in flight together -- one round trip and no set-up, where the bulk-copy merge pays for its barrier and
+// its longer code (3.1 us for the two parts of a decode unit, cold).  The arithmetic is the bulk merge's, operation
+// for operation, in part order: the same bits, whichever of the two is used and whichever CTA merges.
+template <typename TOut>
+__device__ __forceinline__ void merge_unit_direct(const SplitKVParams &p, int u, int c_first, int nparts, int t, int nt) {
+  const int kvh = u % p.kv_heads, sb = u / p.kv_heads, blk = sb % p.nblk, s = sb / p.nblk;
+  const int tok0 = blk * p.rb, ntok = min(p.rb, p.n_new - tok0);
+  const int R = ntok * GROUP, rs = p.rb * GROUP;
+  const float *base = p.ws + (size_t)(c_first + u) * rs * PART_STRIDE;
+  for (int idx = t; idx < R * 32; idx += nt) {
+    const int row = idx >> 5, c8 = idx & 31;
+    float m[4], l[4];
+    float4 va[4], vb[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      m[k] = -INFINITY;
+      l[k] = 0.f;
+      va[k] = vb[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < nparts) {
+        const float *src = base + ((size_t)k * rs + row) * PART_STRIDE;
+        m[k] = __ldcg(src + 256);
+        l[k] = __ldcg(src + 257);
+        va[k] = __ldcg(reinterpret_cast<const float4 *>(src + c8 * 8));
+        vb[k] = __ldcg(reinterpret_cast<const float4 *>(src + c8 * 8 + 4));
+      }
+    }
+    const size_t gr = ((size_t)s * p.n_new + tok0 + row / GROUP) * p.q_heads + (size_t)kvh * GROUP + row % GROUP;
+    uint4 g4 = make_uint4(0, 0, 0, 0);
+    if (!p.partial_out && p.do_gate) g4 = *reinterpret_cast<const uint4 *>(p.gate + gr * HEAD_DIM + c8 * 8);
+    float m_run = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) m_run = fmaxf(m_run, l[k] > 0.f ? m[k] : -INFINITY);
+    float l_run = 0.f;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (k >= nparts) continue;
+      const float f = l[k] > 0.f ? fast_exp2(m[k] - m_run) : 0.f;
+      l_run = fmaf(l[k], f, l_run);
+      v[0] = fmaf(va[k].x, f, v[0]); v[1] = fmaf(va[k].y, f, v[1]); v[2] = fmaf(va[k].z, f, v[2]); v[3] = fmaf(va[k].w, f, v[3]);
+      v[4] = fmaf(vb[k].x, f, v[4]); v[5] = fmaf(vb[k].y, f, v[5]); v[6] = fmaf(vb[k].z, f, v[6]); v[7] = fmaf(vb[k].w, f, v[7]);
+    }
+    if (p.partial_out) {
+      float *dst = p.partial_out + gr * PART_STRIDE;
+      *reinterpret_cast<float4 *>(dst + c8 * 8) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4 *>(dst + c8 * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      if (c8 == 0) { dst[256] = m_run; dst[257] = l_run; }
+      continue;
+    }
+    const float inv = __fdividef(1.f, l_run);
+    const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j] *= inv;
+      if (p.do_gate) v[j] *= sigmoid_fast((j & 1) ? bf16hi(gw[j >> 1]) : bf16lo(gw[j >> 1]));
+    }
+    store8<TOut>(reinterpret_cast<TOut *>(p.out) + gr * HEAD_DIM + c8 * 8, v);
+    if (c8 == 0 && p.lse) p.lse[gr] = (m_run + log2f(l_run)) * LN2;
+  }
+}
+
 // Merge of one unit by ALL the CTAs that hold a part of it, each taking a slice of the (row, 4-channel) items: for
 // a unit cut into dozens of parts (one sequence alone on the whole device: 37) a single merging CTA has to pull every
 // part -- 231 KB -- through one SM, which costs more than the streaming of the sequence's KV; sliced, a CTA reads
@@ -1120,7 +1182,9 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       continue;            // the counter is left as it is: other CTAs of the unit may still be reading it
     }
     if (!pend[5 * k + 4]) continue;  // (sliced variant, unit merged the plain way: not this CTA's)
-    if (total >= (long long)G && merge_bulk_fits(p, R, np, MERGE_BUF)) {
+    if (total >= (long long)G && np <= 4) {
+      merge_unit_direct<TOut>(p, um, cf, np, tid, NCT);
+    } else if (total >= (long long)G && merge_bulk_fits(p, R, np, MERGE_BUF)) {
       if (!merge_unit_bulk<TOut>(p, um, cf, np, tid, NCT, smem, MERGE_BUF, merge_bar, merge_phase) && tid == 0 && p.status)
         *p.status = DEV_ERR_FULL_WAIT;
     } else {
