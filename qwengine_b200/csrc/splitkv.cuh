@@ -491,70 +491,74 @@ __device__ __forceinline__ void merge_unit_direct(const SplitKVParams &p, int u,
 // Merge of one unit by ALL the CTAs that hold a part of it, each taking a slice of the (row, 4-channel) items: for
 // a unit cut into dozens of parts (one sequence alone on the whole device: 37) a single merging CTA has to pull every
 // part -- 231 KB -- through one SM, which costs more than the streaming of the sequence's KV; sliced, a CTA reads
-// 1/nparts of every part.  The caller has waited until every part has arrived.  One warp per item, lanes over the
-// parts (up to five each): all loads of two items are in flight together, then the row maximum, the weights and
-// the weighted sums are reduced across the lanes in a fixed tree, so the result does not depend on timing.
-// j: this CTA's index among the unit's nparts CTAs (nparts <= 160).
-template <typename TOut>
-__device__ __forceinline__ void merge_unit_sliced(const SplitKVParams &p, int u, int c_first, int nparts, int j, int warp,
-                                                  int lane, int nwarps) {
+// 1/nparts of every part.  The caller has waited until every part has arrived.  A group of 8, 16 or 32 lanes (the
+// power of two that holds the parts; beyond 32 a lane takes up to five) serves one item, a warp 4, 2 or 1 items at a
+// time and several such rounds per iteration: all loads of an iteration are in flight together, then the row maximum,
+// the weights and the weighted sums are reduced across the group's lanes in a fixed tree, so the result does not
+// depend on timing.  j: this CTA's index among the unit's nparts CTAs (nparts <= 160).
+// LG: lanes per item (a power of two that holds the parts, or 32); PL: parts per lane; UN: rounds per iteration
+// (their loads are all in flight together).
+template <typename TOut, int LG, int PL, int UN>
+__device__ __forceinline__ void merge_unit_sliced_t(const SplitKVParams &p, int u, int c_first, int nparts, int j, int warp,
+                                                    int lane, int nwarps) {
   const int kvh = u % p.kv_heads, sb = u / p.kv_heads, blk = sb % p.nblk, s = sb / p.nblk;
   const int tok0 = blk * p.rb, ntok = min(p.rb, p.n_new - tok0);
   const int R = ntok * GROUP, rs = p.rb * GROUP, n_items = R * 64;
   const int lo = (int)((long long)n_items * j / nparts), hi = (int)((long long)n_items * (j + 1) / nparts);
   const float *base = p.ws + (size_t)(c_first + u) * rs * PART_STRIDE;  // part k, row r: base + (k * rs + r) * PART_STRIDE
-  constexpr int PL = 5;
-  for (int it0 = lo + warp * 2; it0 < hi; it0 += nwarps * 2) {
-    float m[2][PL], l[2][PL];
-    float4 v[2][PL];
-    uint2 g2[2];
+  constexpr int g = LG, per_round = 32 / LG;
+  const int sub = lane / g, pl = lane % g;
+  for (int it0 = lo + warp * UN * per_round; it0 < hi; it0 += nwarps * UN * per_round) {
+    float m[UN][PL], l[UN][PL];
+    float4 v[UN][PL];
+    uint2 g2[UN];
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int item = it0 + e, r = item >> 6, c4 = item & 63;
+    for (int e = 0; e < UN; ++e) {
+      const int item = it0 + e * per_round + sub, r = item >> 6, c4 = item & 63;
       g2[e] = make_uint2(0, 0);
 #pragma unroll
-      for (int q = 0; q < PL; ++q) {
-        const int k = lane + 32 * q;
-        m[e][q] = -INFINITY;
-        l[e][q] = 0.f;
-        v[e][q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (item < hi && k < nparts) {
+      for (int q2 = 0; q2 < PL; ++q2) {
+        const int k = pl + g * q2;
+        m[e][q2] = -INFINITY;
+        l[e][q2] = 0.f;
+        v[e][q2] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (item < hi && k < nparts && (q2 == 0 || g == 32)) {
           const float *src = base + ((size_t)k * rs + r) * PART_STRIDE;
-          m[e][q] = __ldcg(src + 256);
-          l[e][q] = __ldcg(src + 257);
-          v[e][q] = __ldcg(reinterpret_cast<const float4 *>(src + c4 * 4));
+          m[e][q2] = __ldcg(src + 256);
+          l[e][q2] = __ldcg(src + 257);
+          v[e][q2] = __ldcg(reinterpret_cast<const float4 *>(src + c4 * 4));
         }
       }
-      if (item < hi && lane == 0 && !p.partial_out && p.do_gate) {
+      if (item < hi && pl == 0 && !p.partial_out && p.do_gate) {
         const size_t gr = ((size_t)s * p.n_new + tok0 + r / GROUP) * p.q_heads + (size_t)kvh * GROUP + r % GROUP;
         g2[e] = *reinterpret_cast<const uint2 *>(p.gate + gr * HEAD_DIM + c4 * 4);
       }
     }
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int item = it0 + e, r = item >> 6, c4 = item & 63;
-      if (item >= hi) continue;  // uniform over the warp
+    for (int e = 0; e < UN; ++e) {
+      const int item = it0 + e * per_round + sub, r = item >> 6, c4 = item & 63;
+      // every lane takes part in the shuffles, whether its group's item exists or not
       float m_run = -INFINITY;
 #pragma unroll
-      for (int q = 0; q < PL; ++q) m_run = fmaxf(m_run, l[e][q] > 0.f ? m[e][q] : -INFINITY);
+      for (int q2 = 0; q2 < PL; ++q2) m_run = fmaxf(m_run, l[e][q2] > 0.f ? m[e][q2] : -INFINITY);
 #pragma unroll
-      for (int o = 16; o; o >>= 1) m_run = fmaxf(m_run, __shfl_xor_sync(0xffffffffu, m_run, o));
+      for (int o = g >> 1; o; o >>= 1) m_run = fmaxf(m_run, __shfl_xor_sync(0xffffffffu, m_run, o));
       float l_run = 0.f;
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int q = 0; q < PL; ++q) {
-        const float f = l[e][q] > 0.f ? fast_exp2(m[e][q] - m_run) : 0.f;
-        l_run = fmaf(l[e][q], f, l_run);
-        a.x = fmaf(v[e][q].x, f, a.x); a.y = fmaf(v[e][q].y, f, a.y);
-        a.z = fmaf(v[e][q].z, f, a.z); a.w = fmaf(v[e][q].w, f, a.w);
+      for (int q2 = 0; q2 < PL; ++q2) {
+        const float f = l[e][q2] > 0.f ? fast_exp2(m[e][q2] - m_run) : 0.f;
+        l_run = fmaf(l[e][q2], f, l_run);
+        a.x = fmaf(v[e][q2].x, f, a.x); a.y = fmaf(v[e][q2].y, f, a.y);
+        a.z = fmaf(v[e][q2].z, f, a.z); a.w = fmaf(v[e][q2].w, f, a.w);
       }
 #pragma unroll
-      for (int o = 16; o; o >>= 1) {
+      for (int o = g >> 1; o; o >>= 1) {
         l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
         a.x += __shfl_xor_sync(0xffffffffu, a.x, o); a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
         a.z += __shfl_xor_sync(0xffffffffu, a.z, o); a.w += __shfl_xor_sync(0xffffffffu, a.w, o);
       }
-      if (lane != 0) continue;
+      if (item >= hi || pl != 0) continue;  // (no shuffle follows in this round)
       const size_t gr = ((size_t)s * p.n_new + tok0 + r / GROUP) * p.q_heads + (size_t)kvh * GROUP + r % GROUP;
       if (p.partial_out) {
         float *dst = p.partial_out + gr * PART_STRIDE;
@@ -577,6 +581,13 @@ __device__ __forceinline__ void merge_unit_sliced(const SplitKVParams &p, int u,
       if (c4 == 0 && p.lse) p.lse[gr] = (m_run + log2f(l_run)) * LN2;
     }
   }
+}
+template <typename TOut>
+__device__ __forceinline__ void merge_unit_sliced(const SplitKVParams &p, int u, int c_first, int nparts, int j, int warp,
+                                                  int lane, int nwarps) {
+  if (nparts > 16) merge_unit_sliced_t<TOut, 32, 5, 2>(p, u, c_first, nparts, j, warp, lane, nwarps);
+  else if (nparts > 8) merge_unit_sliced_t<TOut, 16, 1, 2>(p, u, c_first, nparts, j, warp, lane, nwarps);
+  else merge_unit_sliced_t<TOut, 8, 1, 2>(p, u, c_first, nparts, j, warp, lane, nwarps);
 }
 
 // FOLD = false: a dedicated producer warp (warp NCW).  FOLD = true: lane 0 of consumer warp 0 also
