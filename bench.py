@@ -760,8 +760,9 @@ def measure_mixed(args, rank, world, peaks, ex_cls):
 def measure_prefill32k_full(args, rank, world, peaks):
     """BASELINE configuration 4, strong-scaled: one 32768-token prompt in 16 chunks of 2048, append then attend.
     1 GPU: all four KV heads; 2 and 4 GPUs: KV-head shards (no exchange); 8 GPUs: one KV head per GPU pair and
-    the pair splits every chunk's query rows zig-zag (rows [0, 512) and [1536, 2048) on one GPU, [512, 1536) on the
-    other: equal causal work), both GPUs appending the whole chunk's K/V: no exchange either."""
+    the pair splits every chunk's query rows zig-zag (rows [0, 512) and [1536, 2048) on one GPU -- one call of two
+    "sequences" over the same cache rows -- and [512, 1536) on the other: equal causal work), both GPUs appending the
+    whole chunk's K/V: no exchange either."""
     from qwengine_b200 import api
     T, CH = 32768, 2048
     kvh = {1: 4, 2: 2, 4: 1, 8: 1}[world]
@@ -781,6 +782,19 @@ def measure_prefill32k_full(args, rank, world, peaks):
             ma.bind_append_only(kc, vc, torch.tensor([c0], dtype=torch.int32, device="cuda"), k[c0:c0 + CH].view(1, CH, kvh, 256),
                                 v[c0:c0 + CH].view(1, CH, kvh, 256))
             calls.append(ma)
+        if half == 0:
+            # This GPU's two row blocks go out as ONE call of two "sequences" that share the cache rows and differ in
+            # position: a launch of one 512-row block is 12 items for 74 CTA pairs, and two launches one after the
+            # other took twice as long as the 4-GPU plan's whole chunk.  The rank holds just its own rows, packed.
+            mx = api.Mixer(2, 512, kv_heads=kvh)
+            sl = slice(c0, c0 + 1024)   # (synthetic data: any 1024 rows of the rank's tensors stand for its two blocks)
+            mx.bind(q[sl].view(2, 512, 6 * kvh, 256), kc, vc,
+                    torch.tensor([c0, c0 + 1536], dtype=torch.int32, device="cuda"), out[sl].view(2, 512, 6 * kvh, 256),
+                    gate=gate[sl].view(2, 512, 6 * kvh, 256), cache_row=torch.zeros(2, dtype=torch.int64, device="cuda"),
+                    flags=api.F_ROPE | api.F_GATE)
+            calls.append(mx)
+            plan.append(calls)
+            continue
         for off, n in blocks:
             r0 = c0 + off
             mx = api.Mixer(1, n, kv_heads=kvh)

@@ -167,6 +167,23 @@ def test_query_rows_of_a_chunk_split_zigzag_between_two_shares(hist, CH):
         ma = api.Mixer(1, CH, kv_heads=1)
         ma.bind_append_only(kc, vc, torch.tensor([hist], dtype=torch.int32, device="cuda"), dev_bf16(c.k), dev_bf16(c.v))
         ma.forward()
+        if len(blocks) == 2:
+            # the share with two row blocks sends them as ONE call of two "sequences" over the same cache rows
+            n = blocks[0][1]
+            pack = lambda x: torch.stack([x[0, off:off + n] for off, _ in blocks]).contiguous()
+            o2 = torch.zeros(2, n, 6, 256, dtype=torch.float32, device="cuda")
+            l2 = torch.zeros(2, n, 6, dtype=torch.float32, device="cuda")
+            mx = api.Mixer(2, n, kv_heads=1)
+            mx.bind(pack(q), kc, vc, torch.tensor([hist + off for off, _ in blocks], dtype=torch.int32, device="cuda"), o2,
+                    gate=pack(gate), lse=l2, cache_row=torch.zeros(2, dtype=torch.int64, device="cuda"),
+                    flags=api.F_ROPE | api.F_GATE)
+            mx.forward()
+            torch.cuda.synchronize()
+            mx.check_status()
+            for i, (off, _) in enumerate(blocks):
+                out[0, off:off + n] = o2[i]
+                lse[0, off:off + n] = l2[i]
+            blocks = []
         for off, n in blocks:
             mx = api.Mixer(1, n, kv_heads=1)
             sl = slice(off, off + n)
