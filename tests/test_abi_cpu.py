@@ -92,3 +92,16 @@ def test_workspace_errors_come_before_any_launch():
     # the same holds for the drop-in decode launcher when ctx is too small for one partial
     assert l.qw_attn_decode_bf16(p, p, p, p, p, 256, 4, 24, 0.0625, p, 16, 1, None) == 4
     assert l.qw_last_launch_count() == 0
+
+
+def test_flag_values_of_the_binding_match_the_header():
+    """qwengine_b200/api.py repeats the QW_F_* values of include/qwengine_attn.h: they must agree, and no two flags
+    may share a bit."""
+    text = open(os.path.join(ROOT, "include", "qwengine_attn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    header = {m.group(1): int(m.group(2)) for m in re.finditer(r"\bQW_F_([A-Z0-9_]+)\s*=\s*(\d+)", text)}
+    assert len(header) >= 9
+    for name, value in header.items():
+        assert getattr(api, "F_" + name) == value, name
+    bits = sorted(header.values())
+    assert all(v & (v - 1) == 0 for v in bits) and len(set(bits)) == len(bits)
