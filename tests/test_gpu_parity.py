@@ -135,6 +135,24 @@ def test_few_long_sequences_merge_sliced_or_by_the_last_cta(hist):
     assert np.array_equal(s1[0], s2[0]) and np.array_equal(s1[1], s2[1])
 
 
+@pytest.mark.parametrize("hist,n_new", [([6000], 4), ([2500, 4000], 3), ([9000], 12)])
+def test_few_long_sequences_with_draft_tokens_both_merge_routes(hist, n_new):
+    """The tcgen05 split-KV kernel with few long units: all CTAs of a unit merge it together, or (QW_F_NO_GRID_WAIT)
+    the CTA that arrives last does; both against the oracle, each bit-identical from run to run."""
+    c = Case(70 + n_new, hist, n_new)
+    _full_check(c, "verify, sliced merge hist=%s" % hist)
+    ref, lse_ref, _, _ = c.oracle()
+    fl = api.F_ROPE | api.F_APPEND | api.F_GATE | api.F_NO_GRID_WAIT
+    a = run_case(c, out_f32=True, flags=fl)
+    b = run_case(c, out_f32=True, flags=fl)
+    assert api.last_attention_kernel() == "splitkv_umma_kernel"
+    check_out(a[0], ref, "verify, no grid wait")
+    check_lse(a[1], lse_ref, "verify, no grid wait")
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    s1, s2 = run_case(c, out_f32=True), run_case(c, out_f32=True)
+    assert np.array_equal(s1[0], s2[0]) and np.array_equal(s1[1], s2[1])
+
+
 def test_config3_shape_reduced():
     """BASELINE config 3 shape: 8 sequences x 4 draft tokens, ragged histories."""
     rng = np.random.default_rng(41)
