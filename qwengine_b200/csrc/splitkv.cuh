@@ -623,6 +623,8 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
   long long *seg = reinterpret_cast<long long *>(empty + STAGES);  // [0]=total [1]=pre(u_first) [2]=u_first
   volatile int *ticket = reinterpret_cast<volatile int *>(seg + 3);
   uint64_t *merge_bar = reinterpret_cast<uint64_t *>(seg + 4);  // two: bulk copies of a merge's parts land on them
+  // MT == 1: 16 KB more, so that the four key slices of a unit of at most eight rows have a buffer each in any segment
+  float *comb_extra = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(seg) + 120 + 15) & ~uintptr_t(15));
   volatile int *pend = reinterpret_cast<volatile int *>(seg + 6);  // units this CTA is to merge: 5 ints each, [10] their count, [11] scratch
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -1039,7 +1041,23 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
         }
       consumer_sync(NCT);
     }
-    for (int k = 0; k < SK_KS && !last_seg; ++k) {
+    // Earlier segments of a CTA (it takes several units, or the tail of one and the head of the next): the ring
+    // already holds the next segment's tiles.  A unit of at most eight rows (one new token per sequence: six) still
+    // gets a buffer per slice -- two in the Q region, which is idle until the next segment stages its rows, two in
+    // 16 KB set aside for this -- and so one barrier here as well.  Same additions, same order, same bits.
+    const bool small = MT == 1 && !last_seg && R <= 8;
+    float *const sb = ks < 2 ? comb + ks * (8 * HEAD_DIM) : comb_extra + (ks - 2) * (8 * HEAD_DIM);
+    if (small) {
+      if (MT == 1) {
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) {
+          const int d = ds * DW + n * 8 + ql * 2;
+          *reinterpret_cast<float2 *>(sb + qd * HEAD_DIM + (d ^ ((qd & 7) << 3))) = make_float2(o[0][n][0], o[0][n][1]);
+        }
+      }
+      consumer_sync(NCT);
+    }
+    for (int k = 0; k < SK_KS && !last_seg && !small; ++k) {
       if (ks == k) {
         // all loads of the round first, then all stores: read-add-write per element would serialise on
         // shared-memory latency (32 dependent round trips per thread and round)
@@ -1087,6 +1105,16 @@ splitkv_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__
       const float4 *srcp = reinterpret_cast<const float4 *>((last_seg ? reinterpret_cast<const float *>(stage_base) : comb) +
                                                             row * HEAD_DIM + ((c8 * 8) ^ ((row & 7) << 3)));
       float4 a = srcp[0], bq = srcp[1];
+      if (small) {
+        const int off = row * HEAD_DIM + ((c8 * 8) ^ ((row & 7) << 3));
+#pragma unroll
+        for (int k = 1; k < SK_KS; ++k) {
+          const float4 *wp = reinterpret_cast<const float4 *>((k < 2 ? comb + k * (8 * HEAD_DIM) : comb_extra + (k - 2) * (8 * HEAD_DIM)) + off);
+          const float4 wa = wp[0], wb = wp[1];
+          a.x += wa.x; a.y += wa.y; a.z += wa.z; a.w += wa.w;
+          bq.x += wb.x; bq.y += wb.y; bq.z += wb.z; bq.w += wb.w;
+        }
+      }
       if (last_seg) {
 #pragma unroll
         for (int k = 1; k < SK_KS; ++k) {
@@ -1379,7 +1407,7 @@ __global__ void __launch_bounds__(256) combine_partials_peer_kernel(const float 
 template <int MT, int DS, int STAGES>
 constexpr size_t splitkv_smem_bytes() {
   return 1024 + (size_t)STAGES * SK_STAGE_BYTES + (size_t)MT * 16 * 1024 + 2 * SK_KS * MT * 16 * 4 +
-         2 * STAGES * 8 + 3 * 8 + 96;
+         2 * STAGES * 8 + 3 * 8 + 96 + (MT == 1 ? 16 + 16384 : 0);
 }
 
 }  // namespace qwb
