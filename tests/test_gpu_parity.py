@@ -504,3 +504,32 @@ def test_launch_with_status_word_already_set_does_nothing(hist, n_new):
     mx.check_status()
     ref, _, _, _ = c.oracle()
     check_out(host_f32(out).reshape(-1, 24, 256), ref, "after clearing the status word")
+
+
+@pytest.mark.parametrize("seed", [11, 12])
+def test_seeded_random_shapes_against_the_oracle(seed):
+    """Forty seeded draws of (sequences, new tokens, KV heads, histories, M-RoPE, QW_F_NO_GRID_WAIT) through the fused
+    call: appended rows bit-exact, output and LSE within the stated tolerance, and a second run bit-identical.  The
+    draws reach both split-KV kernels and every merge route (direct, bulk, row, sliced)."""
+    rng = np.random.default_rng(seed)
+    kernels = set()
+    for _ in range(40):
+        n_seq = int(rng.choice([1, 1, 2, 3, 4, 7, 16]))
+        n_new = int(rng.choice([1, 1, 1, 2, 4, 5, 6, 12, 21, 40, 63]))
+        kvh = int(rng.choice([4, 4, 2, 1]))
+        top = int(rng.choice([300, 3000, 12000])) if n_seq <= 4 else int(rng.choice([300, 2000]))
+        hist = rng.integers(0, top, n_seq).tolist()
+        if n_seq * (max(hist) + n_new) * n_new > 1.5e6:  # keeps the oracle to a fraction of a second
+            hist = [h % 1500 for h in hist]
+        flags = api.F_ROPE | api.F_APPEND | api.F_GATE | api.F_NO_GRID_WAIT if rng.random() < 0.3 else None
+        c = Case(int(rng.integers(1 << 30)), hist, n_new, kv_heads=kvh, mrope=bool(rng.random() < 0.2))
+        what = "n_seq=%d n_new=%d kv_heads=%d hist=%s flags=%s" % (n_seq, n_new, kvh, hist, flags)
+        ref, lse_ref, kc_ref, vc_ref = c.oracle()
+        o, lse, kc, vc, _ = run_case(c, out_f32=True, flags=flags)
+        assert np.array_equal(kc, kc_ref) and np.array_equal(vc, vc_ref), what
+        check_out(o, ref, what)
+        check_lse(lse, lse_ref, what)
+        again = run_case(c, out_f32=True, flags=flags)
+        assert np.array_equal(o, again[0]) and np.array_equal(lse, again[1]), "not repeatable: " + what
+        kernels.add(api.last_attention_kernel())
+    assert kernels == {"splitkv_kernel", "splitkv_umma_kernel"}
