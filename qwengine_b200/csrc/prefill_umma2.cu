@@ -749,7 +749,10 @@ prefill_umma_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_
     if (have) stage_q(w, 0);
     for (int k = 0; have && ok; ++k) {
       const int nt = w.nt, pos = w.pos, q0 = w.q0;
-      const int qpos = pos + q0 + row;  // causal limit: keys 0 .. qpos
+      // Causal limit: keys 0 .. qpos.  Rows past the chunk's end take the last row's limit, so that no score of a
+      // key outside the sequence enters a row maximum: the rescale vote below is per warp, and the result would
+      // otherwise depend, in its last bits, on whatever lies behind the sequence's rows in the cache.
+      const int qpos = pos + q0 + min(row, w.rows_valid - 1);
       float m_used = -INFINITY, l_run = 0.f;
       for (int j = 0; j < nt; ++j) {
         const int g = G + j;

@@ -59,6 +59,8 @@ CASES = {
     "short_chunk_2kv": (Case, (203, [260], 20), {"kv_heads": 2}),
     "prefill_chunk_hist": (Case, (204, [300], 160), {"kv_heads": 2}),
     "prefill_scratch": (Case, (205, [0], 384), {"kv_heads": 2}),
+    # the last 128-row tile of the first sequence is part empty, and another sequence's rows lie behind it
+    "prefill_two_sequences_ragged_tile": (Case, (206, [114, 134], 300), {"kv_heads": 1}),
 }
 
 
