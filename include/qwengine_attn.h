@@ -90,8 +90,11 @@ int qw_kv_append_f32(const float *k, const float *v, qw_bf16 *kc, qw_bf16 *vc,
  * reference's own kernel needs at the same launch (src/mixers.cu:441, rt.scores at
  * src/model.cu:168, M.scores at src/mtp.cu:115).  The launcher uses exactly that many floats
  * (qw_attn_decode_scratch_floats() returns the same number) for split-KV partials and
- * arrival counters: the more there are, the more CTAs share a sequence; if they do not
- * even hold one CTA's partial (ctx below about 128) the call returns QW_ERR_WORKSPACE.
+ * arrival counters: the more there are, the more CTAs share a sequence.  If they do not hold
+ * even one set of partials (ctx below about 370: the reference sizes ctx as prompt + new
+ * tokens + 8, src/main.cu:38, so short runs get there) the launcher leaves `scratch` untouched
+ * and keeps the partials in the library's own fixed device array, the one
+ * qw_attn_decode_bf16_noalloc uses.
  * ctx is the number of rows in kc / vc.  1 <= B <= 8.  The bf16 flavour runs B >= 2 on the
  * tcgen05 split-KV kernel; the fp32 flavour keeps q exact (bf16 hi + lo on all channels)
  * on the mma.sync kernel.  These launchers serve one sequence, so they take the kernel variant

@@ -509,6 +509,33 @@ int mixer_forward_impl(const qw_mixer_desc *d, float *partial, cudaStream_t st, 
   return sp.umma ? launch_splitkv_umma_call(c, st) : launch_splitkv(c, st);
 }
 
+// ---- allocation-free decode: split-KV partials in a fixed array inside the library image --------
+// Sized for the largest request the entry point accepts: B <= 8 tokens (two unit blocks of <= 5)
+// and kv_heads <= 4 give at most 8 units; up to 160 CTAs; one slot = 5 tokens x 6 heads x 260 floats.
+constexpr int NOALLOC_MAX_B = 8;
+constexpr int NOALLOC_MAX_KV_HEADS = 4;
+constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)(160 + 2 * NOALLOC_MAX_KV_HEADS) * 5 * GROUP * PART_STRIDE;
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+
+// In host code the name g_noalloc_scratch is only a handle for the symbol, not an address a kernel
+// could use.  The device address is looked up once per device, with that device current.
+int noalloc_scratch_address(float **out) {
+  static std::mutex mu;
+  static float *addr[MAX_DEVICES] = {nullptr};
+  int dev = 0;
+  QW_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) return QW_ERR_ARG;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void *p = nullptr;
+    QW_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    if (!p) return QW_ERR_CUDA;
+    addr[dev] = static_cast<float *>(p);
+  }
+  *out = addr[dev];
+  return QW_OK;
+}
+
 // Drop-in attention launchers share this: one sequence, rows already rotated and appended
 // (src/model.cu:228-236, src/prefill.cu:142-152 of the reference run rope and k_kv_append first).
 //   chunks of >= 64 rows      tcgen05 CTA-pair prefill kernel (an fp32 q is first copied to bf16 in scratch)
@@ -556,7 +583,25 @@ int attn_dropin(const T *q, const qw_bf16 *kc, const qw_bf16 *vc, T *out, const 
   }
   const SplitPlan sp = split_plan(1, rows, kv_heads, !F32);
   const size_t cnt_bytes = mixer_cnt_bytes(1, rows, kv_heads);
-  if (have * sizeof(float) <= cnt_bytes) return QW_ERR_WORKSPACE;
+  const bool scratch_short = have * sizeof(float) <= cnt_bytes ||
+                             (long long)((have - cnt_bytes / sizeof(float)) / sp.slot) - sp.units < 1;
+  if (scratch_short && decode) {
+    // A cache of a few hundred rows (the reference sizes ctx as prompt + new tokens + 8, src/main.cu:38) makes
+    // the reference's score buffer smaller than one set of split-KV partials.  The partials then go to the
+    // library's own fixed array, as in the allocation-free entry point, and the caller's scratch stays untouched.
+    float *own = nullptr;
+    int rc = noalloc_scratch_address(&own);
+    if (rc) return rc;
+    AttnCall c;
+    memset(&c, 0, sizeof(c));
+    c.q = q; c.q_is_f32 = F32; c.out = out; c.out_is_f32 = F32;
+    c.kc = kc; c.vc = vc; c.cache_rows = ctx; c.pos = dpos;
+    c.n_seq = 1; c.n_new = rows; c.q_heads = q_heads; c.kv_heads = kv_heads;
+    c.theta = 1e7f; c.scale = scale;
+    c.ws = own; c.ws_floats = NOALLOC_SCRATCH_FLOATS;
+    return launch_splitkv(c, st);
+  }
+  if (scratch_short) return QW_ERR_WORKSPACE;
   AttnCall c;
   memset(&c, 0, sizeof(c));
   c.q = q; c.q_is_f32 = F32; c.out = out; c.out_is_f32 = F32;
@@ -566,36 +611,8 @@ int attn_dropin(const T *q, const qw_bf16 *kc, const qw_bf16 *vc, T *out, const 
   c.cnt = reinterpret_cast<int *>(scratch);
   c.ws = scratch + cnt_bytes / sizeof(float);
   c.ws_floats = have - cnt_bytes / sizeof(float);
-  if ((long long)(c.ws_floats / sp.slot) - sp.units < 1) return QW_ERR_WORKSPACE;
   QW_CUDA(cudaMemsetAsync(c.cnt, 0, cnt_bytes, st));
   return sp.umma ? launch_splitkv_umma_call(c, st) : launch_splitkv(c, st);
-}
-
-// ---- allocation-free decode: split-KV partials in a fixed array inside the library image --------
-// Sized for the largest request the entry point accepts: B <= 8 tokens (two unit blocks of <= 5)
-// and kv_heads <= 4 give at most 8 units; up to 160 CTAs; one slot = 5 tokens x 6 heads x 260 floats.
-constexpr int NOALLOC_MAX_B = 8;
-constexpr int NOALLOC_MAX_KV_HEADS = 4;
-constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)(160 + 2 * NOALLOC_MAX_KV_HEADS) * 5 * GROUP * PART_STRIDE;
-static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
-
-// In host code the name g_noalloc_scratch is only a handle for the symbol, not an address a kernel
-// could use.  The device address is looked up once per device, with that device current.
-int noalloc_scratch_address(float **out) {
-  static std::mutex mu;
-  static float *addr[MAX_DEVICES] = {nullptr};
-  int dev = 0;
-  QW_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= MAX_DEVICES) return QW_ERR_ARG;
-  std::lock_guard<std::mutex> lock(mu);
-  if (!addr[dev]) {
-    void *p = nullptr;
-    QW_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
-    if (!p) return QW_ERR_CUDA;
-    addr[dev] = static_cast<float *>(p);
-  }
-  *out = addr[dev];
-  return QW_OK;
 }
 
 }  // namespace

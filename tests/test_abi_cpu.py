@@ -89,9 +89,8 @@ def test_workspace_errors_come_before_any_launch():
         d.workspace, d.workspace_bytes = ws, nbytes
         assert l.qw_mixer_forward(ctypes.byref(d), None) == 4
         assert l.qw_last_launch_count() == 0
-    # the same holds for the drop-in decode launcher when ctx is too small for one partial
-    assert l.qw_attn_decode_bf16(p, p, p, p, p, 256, 4, 24, 0.0625, p, 16, 1, None) == 4
-    assert l.qw_last_launch_count() == 0
+    # (the drop-in decode launcher has no such error: with a scratch too small for one set of partials it uses the
+    # library's own array, tests/test_gpu_parity.py::test_dropin_decode_with_a_cache_of_a_few_rows)
 
 
 def test_flag_values_of_the_binding_match_the_header():

@@ -322,6 +322,38 @@ def test_dropin_decode_uses_no_more_scratch_than_documented(dtype, B):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("pos0,B,ctx", [(0, 1, 1), (5, 1, 45), (30, 3, 45), (0, 8, 8), (150, 8, 200), (299, 1, 300)])
+def test_dropin_decode_with_a_cache_of_a_few_rows(dtype, pos0, B, ctx):
+    """The reference sizes its cache as prompt + new tokens + 8 rows (src/main.cu:38), so a short run has a score
+    buffer of a few hundred floats, less than one set of split-KV partials.  The launcher then keeps the partials
+    in the library's own array: the result still matches the oracle and the caller's scratch is not written."""
+    c = Case(80 + B + ctx, [pos0], B, pad_rows=ctx - pos0 - B)
+    ref, _, kc_ref, vc_ref = c.oracle(do_gate=False)
+    q = torch.from_numpy(c.q[0]).cuda().to(dtype)
+    k = torch.from_numpy(c.k[0]).cuda().to(dtype)
+    v = torch.from_numpy(c.v[0]).cuda().to(dtype)
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    n = api.attn_decode_scratch_floats(24, 4, ctx, B)
+    assert n == B * 24 * ctx
+    scratch = torch.full((n + 4096,), -7.25, dtype=torch.float32, device="cuda")
+    api.rope(q, 24, 256, 64, dpos, 1e7, B=B)
+    api.rope(k, 4, 256, 64, dpos, 1e7, B=B)
+    api.kv_append(k, v, kc, vc, dpos, 1024, B=B)
+    api.attn_decode(q, kc, vc, out, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, B=B)
+    torch.cuda.synchronize()
+    assert api.last_attention_kernel() == "splitkv_kernel"
+    assert bool((scratch == -7.25).all()), "the launcher wrote into a scratch it had judged too small"
+    assert np.array_equal(host_bits(kc), kc_ref) and np.array_equal(host_bits(vc), vc_ref)
+    got = host_f32(out)
+    if dtype == torch.float32:
+        check_out(got, ref, "drop-in decode, short cache, f32")
+    else:
+        assert np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 4e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("pos0,T,ctx", [(0, 64, 256), (300, 256, 1024), (1000, 333, 2048)])
 def test_dropin_prefill_reaches_the_tcgen05_kernel(dtype, pos0, T, ctx):
     """qw_attn_prefill_* with a chunk of 64 rows or more, as src/prefill.cu:142-154 would call it: rope, append,
