@@ -226,6 +226,24 @@ int main() {
     CK(cudaGraphExecDestroy(exec));
     CK(cudaGraphDestroy(graph));
   }
+  // ---- a short run: the engine sizes its cache as prompt + new tokens + 8 rows (src/main.cu:38), so the score
+  //      buffer of B * q_heads * ctx floats is far smaller than one set of split-KV partials ----
+  for (int bi = 0; bi < 2; ++bi) {
+    const int B = bi == 0 ? 1 : 4, prompt = 5, ctx = prompt + 32 + 8;
+    Site s = make_site(ctx, 8, prompt);
+    int pos = prompt;
+    for (int step = 0; step < 3; ++step) {
+      set_pos(s, pos);
+      new_rows(s, B);
+      record_step_ours(s, B, st);
+      record_step_ref(s, B, st);
+      CK(cudaStreamSynchronize(st));
+      char what[96];
+      snprintf(what, sizeof(what), "short run ctx=%d B=%d pos=%d (src/main.cu:38)", ctx, B, pos);
+      ok = compare(what, s.attn_out, s.ref_out, (size_t)B * Q_DIM, 2e-3) && ok;
+      pos += B;
+    }
+  }
   // ---- prefill: two chunks of one prompt, the second behind the first (src/prefill.cu:231-240) ----
   {
     const int T = 512, ctx = 2048;
