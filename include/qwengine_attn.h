@@ -133,9 +133,10 @@ int qw_attn_decode_bf16_noalloc(const qw_bf16 *q, const qw_bf16 *kc, const qw_bf
 /* Chunked-prefill attention: row t of q[T][q_heads][dim] attends to the first
  * *dpos + t + 1 cache rows.  Chunks of T >= 64 rows run on the tcgen05 CTA-pair kernel,
  * shorter ones on the split-KV kernels.  `scratch` (reference: T * q_heads * ctx floats,
- * src/prefill.cu:75) must hold qw_attn_prefill_scratch_floats() floats, 16-byte aligned
- * (for a short chunk in a small cache that is MORE than the reference's size, and the
- * launcher cannot check a size it is not given: size the allocation by that function):
+ * src/prefill.cu:75), 16-byte aligned, holds either the reference's size or
+ * qw_attn_prefill_scratch_floats() floats: the launcher, which is not told which, writes
+ * no further than the smaller of the two, and where that is too little (a cache of a few
+ * rows) it leaves `scratch` untouched and uses the library's fixed device array.  It holds
  * split-KV partials for short chunks and, in the fp32 flavour with T >= 64, the bf16 copy
  * of q that the tensor cores read (q is rounded to bf16 there, exactly as k is when it
  * enters the bf16 cache; short chunks keep q exact).

@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <mutex>
 
 #include "common.cuh"
@@ -554,17 +555,29 @@ int attn_dropin(const T *q, const qw_bf16 *kc, const qw_bf16 *vc, T *out, const 
   if (!geometry_ok(dim, kv_heads, q_heads)) return QW_ERR_SHAPE;
   if (decode && rows > 8) return QW_ERR_SHAPE;
   if (rows == 0) return QW_OK;
-  const size_t have = decode ? qw_attn_decode_scratch_floats(q_heads, kv_heads, ctx, rows)
-                             : qw_attn_prefill_scratch_floats(q_heads, kv_heads, ctx, rows);
+  // The launcher is not told how large `scratch` is.  A caller may have sized it as the reference does
+  // (rows * q_heads * ctx floats: src/model.cu:168, src/prefill.cu:75) or, for prefill, by the query function; the
+  // launcher counts on the smaller of the two and, where that does not hold what the call needs (a cache of a few
+  // hundred rows: the reference sizes ctx as prompt + new tokens + 8, src/main.cu:38), leaves `scratch` untouched
+  // and uses the library's own fixed array, as the allocation-free entry point does.
+  const size_t ref_size = (size_t)rows * q_heads * ctx;
+  const size_t have = decode ? ref_size : std::min(ref_size, qw_attn_prefill_scratch_floats(q_heads, kv_heads, ctx, rows));
   if (!decode && prefill_umma_supported(rows)) {
     const uint16_t *qb = reinterpret_cast<const uint16_t *>(q);
     if (F32) {
       const long long n = (long long)rows * q_heads * HEAD_DIM;
-      to_bf16_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const float *>(q),
-                                                                     reinterpret_cast<uint16_t *>(scratch), n);
+      uint16_t *copy = reinterpret_cast<uint16_t *>(scratch);
+      if (have < (size_t)n / 2) {  // ctx < 128: the bf16 copy of q does not fit the reference-sized buffer
+        if ((size_t)n / 2 > NOALLOC_SCRATCH_FLOATS) return QW_ERR_WORKSPACE;  // not reachable: rows <= ctx < 128
+        float *own = nullptr;
+        int rc = noalloc_scratch_address(&own);
+        if (rc) return rc;
+        copy = reinterpret_cast<uint16_t *>(own);
+      }
+      to_bf16_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const float *>(q), copy, n);
       int rc = check_launch("to_bf16_kernel");
       if (rc) return rc;
-      qb = reinterpret_cast<const uint16_t *>(scratch);
+      qb = copy;
     }
     PrefillCall pc;
     memset(&pc, 0, sizeof(pc));
@@ -585,10 +598,7 @@ int attn_dropin(const T *q, const qw_bf16 *kc, const qw_bf16 *vc, T *out, const 
   const size_t cnt_bytes = mixer_cnt_bytes(1, rows, kv_heads);
   const bool scratch_short = have * sizeof(float) <= cnt_bytes ||
                              (long long)((have - cnt_bytes / sizeof(float)) / sp.slot) - sp.units < 1;
-  if (scratch_short && decode) {
-    // A cache of a few hundred rows (the reference sizes ctx as prompt + new tokens + 8, src/main.cu:38) makes
-    // the reference's score buffer smaller than one set of split-KV partials.  The partials then go to the
-    // library's own fixed array, as in the allocation-free entry point, and the caller's scratch stays untouched.
+  if (scratch_short) {  // not even one set of split-KV partials: they go to the fixed array
     float *own = nullptr;
     int rc = noalloc_scratch_address(&own);
     if (rc) return rc;
@@ -601,7 +611,6 @@ int attn_dropin(const T *q, const qw_bf16 *kc, const qw_bf16 *vc, T *out, const 
     c.ws = own; c.ws_floats = NOALLOC_SCRATCH_FLOATS;
     return launch_splitkv(c, st);
   }
-  if (scratch_short) return QW_ERR_WORKSPACE;
   AttnCall c;
   memset(&c, 0, sizeof(c));
   c.q = q; c.q_is_f32 = F32; c.out = out; c.out_is_f32 = F32;

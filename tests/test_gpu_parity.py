@@ -354,6 +354,35 @@ def test_dropin_decode_with_a_cache_of_a_few_rows(dtype, pos0, B, ctx):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("pos0,T,ctx", [(0, 5, 45), (0, 40, 80), (7, 63, 70), (0, 64, 104), (10, 100, 120), (0, 127, 127)])
+def test_dropin_prefill_with_a_reference_sized_scratch_in_a_small_cache(dtype, pos0, T, ctx):
+    """The prefill launcher is not told the size of its scratch.  A caller that kept the reference's allocation
+    (T * q_heads * ctx floats, src/prefill.cu:75) has, in a cache of a few rows, less than the split-KV partials of a
+    short chunk or (fp32, T >= 64, ctx < 128) the bf16 copy of q need: the launcher must then not write into it."""
+    c = Case(90 + T + ctx, [pos0], T, pad_rows=ctx - pos0 - T)
+    ref, _, kc_ref, vc_ref = c.oracle(do_gate=False)
+    q = torch.from_numpy(c.q[0]).cuda().to(dtype)
+    k = torch.from_numpy(c.k[0]).cuda().to(dtype)
+    v = torch.from_numpy(c.v[0]).cuda().to(dtype)
+    kc, vc = dev_bits(c.kc0), dev_bits(c.vc0)
+    dpos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    n = T * 24 * ctx                      # the reference's size
+    scratch = torch.full((n + (1 << 21),), -7.25, dtype=torch.float32, device="cuda")
+    api.rope(q, 24, 256, 64, dpos, 1e7, B=T)
+    api.rope(k, 4, 256, 64, dpos, 1e7, B=T)
+    api.kv_append(k, v, kc, vc, dpos, 1024, B=T)
+    api.attn_prefill(q, kc, vc, out, dpos, 256, 4, 24, 1.0 / 16.0, scratch, ctx, T)
+    torch.cuda.synchronize()
+    assert bool((scratch[n:] == -7.25).all()), "the launcher wrote past the reference's scratch size"
+    assert api.last_attention_kernel() == ("prefill_umma_pair_kernel" if T >= 64 else "splitkv_kernel")
+    assert np.array_equal(host_bits(kc), kc_ref) and np.array_equal(host_bits(vc), vc_ref)
+    got = host_f32(out)
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= 2e-2 and rel_l2(got, ref) <= 4e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("pos0,T,ctx", [(0, 64, 256), (300, 256, 1024), (1000, 333, 2048)])
 def test_dropin_prefill_reaches_the_tcgen05_kernel(dtype, pos0, T, ctx):
     """qw_attn_prefill_* with a chunk of 64 rows or more, as src/prefill.cu:142-154 would call it: rope, append,
